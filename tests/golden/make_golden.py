@@ -1,0 +1,224 @@
+"""Generates the golden fixtures in this directory by running the REFERENCE itself.
+
+Run once, in a container that has the reference checkout (path given by --reference) and Triton:
+
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py --reference <path to the reference checkout>
+
+Two families of vectors are written (float16/float32 as noted, all tiny):
+
+* ``kernel_*.pt``: the reference's own Triton kernels (``_angular_lsh_kernel``, ``_fwd_hyper_kernel``,
+  the three hyper backward kernels, the flash forward kernel) executed by the Triton interpreter on CPU
+  tensors in float16.  The host launchers assert CUDA, so the ``@triton.jit`` objects are launched
+  directly with the launchers' own argument lists.
+* ``module_*.pt``: the reference's own ``HyperAttention.forward`` (recursion, views, merge, cat, autograd)
+  executed on CPU in float32 with its three device-only callables replaced: ``hash_triton`` by the
+  reference's own ``hash_torch``, and ``hyper_attn_func`` / ``flash_attn_func`` by the oracle's Functions
+  (the mounted reference has no CPU attention kernel).  These pin the orchestration: which calls are made
+  on which slices, how parts are merged, what is returned.
+
+The fixtures hold inputs and outputs, so that the tests need neither the reference nor Triton.
+"""
+import argparse
+import math
+import os
+import sys
+
+os.environ.setdefault('TRITON_INTERPRET', '1')
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+
+def kernel_lsh(ref, out_dir):
+    from src import angular_lsh_triton as L
+    torch.manual_seed(10)
+    for tag, (B, H, n, d, r) in {'a': (1, 2, 256, 64, 8), 'b': (1, 1, 200, 128, 8), 'c': (2, 1, 128, 64, 5)}.items():
+        lsh = L.AngularLSHTriton(num_projs=r, dim=(1, 1, d)).to(dtype=torch.float16)
+        x = torch.randn(B, H, n, d).to(torch.float16)
+        buckets = torch.empty(B, H, n, dtype=torch.int32)
+        BH = max(1 << (d - 1).bit_length(), 16)
+        L._angular_lsh_kernel[(math.ceil(n / 128), B * H)](
+            in_mat=x, proj_dir=lsh.proj_dir, perm=lsh.perm, enc_vec=lsh.enc_vec, buckets=buckets,
+            stride_in_matb=x.stride(0), stride_in_math=x.stride(1), stride_in_matm=x.stride(2),
+            stride_proj_dirb=0, stride_proj_dirh=0, stride_proj_dird=lsh.proj_dir.stride(2),
+            stride_bucketsb=buckets.stride(0), stride_bucketsh=buckets.stride(1), nheads=H, seqlen=n,
+            seqlen_rounded=math.ceil(n / 128) * 128, headdim=d, NUM_PROJ_ROUNDED=16, num_projs=r,
+            BLOCK_HEADDIM=BH, BLOCK_M=128)
+        torch.save({'x': x, 'proj_dir': lsh.proj_dir.clone(), 'perm': lsh.perm.clone(), 'codes_kernel': buckets,
+                    'codes_hash_torch': lsh.hash_torch(x).to(torch.int32)}, os.path.join(out_dir, f'kernel_lsh_{tag}.pt'))
+        print('lsh', tag, 'kernel==hash_torch:', bool((buckets == lsh.hash_torch(x)).all()))
+
+
+def _launch_hyper_fwd(H_, q, k, v, qi, ki, block_size, sample_size, scale, smooth):
+    """q,k,v [B,n,H,d] views; mirrors _hyper_attn_forward's launch (src/hyper_attn_triton.py:668-742)."""
+    B, n, H, d = q.shape
+    dv = v.shape[-1]
+    lse = torch.empty(B, H, n, dtype=torch.float32)
+    o = torch.empty(B, n, H, dv, dtype=q.dtype)
+    p2 = lambda x: max(1 << (x - 1).bit_length(), 16)
+    H_._fwd_hyper_kernel[(n // 128, B * H)](
+        Q=q, K=k, V=v, q_sort_idx=qi, k_sort_idx=ki, Out=o, Lse=lse, softmax_scale=scale,
+        stride_qb=q.stride(0), stride_qh=q.stride(2), stride_qm=q.stride(1),
+        stride_kb=k.stride(0), stride_kh=k.stride(2), stride_kn=k.stride(1),
+        stride_vb=v.stride(0), stride_vh=v.stride(2), stride_vn=v.stride(1),
+        stride_q_sort_idxb=qi.stride(0), stride_q_sort_idxh=qi.stride(2), stride_q_sort_idxm=qi.stride(1),
+        stride_k_sort_idxb=ki.stride(0), stride_k_sort_idxh=ki.stride(2), stride_k_sort_idxn=ki.stride(1),
+        stride_ob=o.stride(0), stride_oh=o.stride(2), stride_om=o.stride(1), nheads=H,
+        block_size=math.ceil(block_size / 128), sample_size=math.ceil(sample_size / 128), seqlen_k=n, seqlen_q=n,
+        headdim=d, v_headdim=dv, smooth_block=int(smooth), CACHE_KEY_SEQLEN_Q=n // 32, CACHE_KEY_SEQLEN_K=n // 32,
+        BLOCK_HEADDIM=p2(d), V_BLOCK_HEADDIM=p2(dv), BLOCK_M=128, BLOCK_N=128)
+    return o, lse
+
+
+def _launch_hyper_bwd(H_, do, q, k, v, qi, ki, o, lse, block_size, sample_size, scale, smooth):
+    """mirrors _hyper_attn_backward's three launches (src/hyper_attn_triton.py:745-892)."""
+    B, n, H, d = q.shape
+    dv_dim = v.shape[-1]
+    p2 = lambda x: max(1 << (x - 1).bit_length(), 16)
+    dq_accum = torch.zeros(B, n, H, d, dtype=torch.float32)
+    dk = torch.zeros_like(k)
+    dvv = torch.zeros_like(v)
+    delta = torch.empty_like(lse)
+    H_._bwd_preprocess_do_o_dot[(n // 128, B * H)](
+        Out=o, DO=do, Delta=delta, stride_ob=o.stride(0), stride_oh=o.stride(2), stride_om=o.stride(1),
+        stride_dob=do.stride(0), stride_doh=do.stride(2), stride_dom=do.stride(1), nheads=H, seqlen_q=n,
+        v_headdim=dv_dim, BLOCK_M=128, V_BLOCK_HEADDIM=p2(dv_dim))
+    common = dict(
+        Q=q, K=k, V=v, DO=do, DQ=dq_accum, DK=dk, DV=dvv, LSE=lse, D=delta, softmax_scale=scale,
+        stride_qb=q.stride(0), stride_qh=q.stride(2), stride_qm=q.stride(1),
+        stride_kb=k.stride(0), stride_kh=k.stride(2), stride_kn=k.stride(1),
+        stride_vb=v.stride(0), stride_vh=v.stride(2), stride_vn=v.stride(1),
+        stride_dob=do.stride(0), stride_doh=do.stride(2), stride_dom=do.stride(1),
+        stride_dqb=dq_accum.stride(0), stride_dqh=dq_accum.stride(2), stride_dqm=dq_accum.stride(1),
+        stride_dkb=dk.stride(0), stride_dkh=dk.stride(2), stride_dkn=dk.stride(1),
+        stride_dvb=dvv.stride(0), stride_dvh=dvv.stride(2), stride_dvn=dvv.stride(1),
+        nheads=H, seqlen_q=n, headdim=d, v_headdim=dv_dim, CACHE_KEY_SEQLEN_Q=n // 32, CACHE_KEY_SEQLEN_K=n // 32,
+        BLOCK_HEADDIM=p2(d), V_BLOCK_HEADDIM=p2(dv_dim), BLOCK_M=128, BLOCK_N=128)
+    H_._bwd_permuted_block_diagonal_kernel[(n // 128, B * H)](
+        q_sort_idx=qi, k_sort_idx=ki,
+        stride_q_sort_idxb=qi.stride(0), stride_q_sort_idxh=qi.stride(2), stride_q_sort_idxm=qi.stride(1),
+        stride_k_sort_idxb=ki.stride(0), stride_k_sort_idxh=ki.stride(2), stride_k_sort_idxn=ki.stride(1),
+        block_size=block_size, smooth_block=int(smooth), **common)
+    if sample_size > 0:
+        H_._bwd_sampled_col_kernel[(math.ceil(sample_size / 128), B * H)](**common)
+    return dq_accum.to(q.dtype), dk, dvv
+
+
+def kernel_hyper(ref, out_dir):
+    from src import hyper_attn_triton as H_
+    torch.manual_seed(11)
+    cases = {
+        # tag: B, H, n, d, dv, block, sample, smooth, with_bwd
+        'plain':   (1, 2, 512, 64, 64, 256, 128, False, True),
+        'smooth':  (1, 2, 512, 64, 64, 256, 128, True, True),
+        'nosamp':  (1, 1, 384, 64, 64, 256, 0, False, True),
+        'd128':    (1, 1, 256, 128, 64, 128, 128, False, False),
+    }
+    for tag, (B, H, n, d, dv, bsz, ssz, smooth, with_bwd) in cases.items():
+        q = torch.randn(B, H, n, d).to(torch.float16)
+        k = torch.randn(B, H, n, d).to(torch.float16)
+        k[:, :, :ssz] *= 2.0
+        v = torch.randn(B, H, n, dv).to(torch.float16)
+        qi = torch.sort(torch.randint(0, 16, (B, H, n)), dim=2, stable=True)[1]
+        ki = torch.sort(torch.randint(0, 16, (B, H, n)), dim=2, stable=True)[1]
+        scale = 1.0 / math.sqrt(d)
+        T = lambda t: t.transpose(1, 2)
+        o, lse = _launch_hyper_fwd(H_, T(q), T(k), T(v), T(qi), T(ki), bsz, ssz, scale, smooth)
+        rec = {'q': q, 'k': k, 'v': v, 'q_sort_idx': qi, 'k_sort_idx': ki, 'block_size': bsz, 'sample_size': ssz,
+               'smooth_block': smooth, 'scale': scale, 'o': T(o).contiguous(), 'lse': lse}
+        if with_bwd:
+            do = torch.randn(B, H, n, dv).to(torch.float16)
+            dq, dk, dvv = _launch_hyper_bwd(H_, T(do), T(q), T(k), T(v), T(qi), T(ki), o, lse, bsz, ssz, scale, smooth)
+            rec.update({'do': do, 'dq': T(dq).contiguous(), 'dk': T(dk).contiguous(), 'dv': T(dvv).contiguous()})
+        torch.save(rec, os.path.join(out_dir, f'kernel_hyper_{tag}.pt'))
+        print('hyper', tag, 'done')
+
+
+def kernel_flash(ref, out_dir):
+    from src import flash_attn_triton as F_
+    torch.manual_seed(12)
+    for tag, (B, H, n, d, causal) in {'causal': (1, 2, 256, 64, True), 'full': (1, 1, 384, 64, False)}.items():
+        q = torch.randn(B, n, H, d).to(torch.float16)
+        k = torch.randn(B, n, H, d).to(torch.float16)
+        v = torch.randn(B, n, H, d).to(torch.float16)
+        n_r = math.ceil(n / 128) * 128
+        lse = torch.empty(B, H, n_r, dtype=torch.float32)
+        o = torch.empty_like(q)
+        scale = 1.0 / math.sqrt(d)
+        F_._fwd_kernel.fn[(math.ceil(n / 128), B * H)](
+            q, k, v, None, o, lse, scale, q.stride(0), q.stride(2), q.stride(1), k.stride(0), k.stride(2), k.stride(1),
+            v.stride(0), v.stride(2), v.stride(1), 0, 0, 0, o.stride(0), o.stride(2), o.stride(1), H, n, n, n_r, d,
+            n // 32, n // 32, 'none', causal, max(1 << (d - 1).bit_length(), 16),
+            EVEN_M=n % 128 == 0, EVEN_N=n % 128 == 0, EVEN_HEADDIM=True, BLOCK_M=128, BLOCK_N=128)
+        torch.save({'q': q, 'k': k, 'v': v, 'causal': causal, 'scale': scale, 'o': o, 'lse': lse[:, :, :n].clone()},
+                   os.path.join(out_dir, f'kernel_flash_{tag}.pt'))
+        print('flash', tag, 'done')
+
+
+def module_cases(ref, out_dir):
+    import hyper_attention as RH
+    from oracle import hyper_oracle as O
+    RH.hyper_attn_func = lambda *a: O.hyper_attn_func(*a)
+    RH.flash_attn_func = lambda q, k, v, bias, causal, scale: O.flash_attn_func(q, k, v, bias, causal, scale)
+    cases = {
+        # tag: B, H, n, d, causal, block, sample, min_seq_len, smooth, seed
+        'c0_noncausal': (1, 4, 4096, 64, False, 256, 256, 2048, False, 0),
+        'causal_2lvl':  (1, 2, 1024, 32, True, 128, 128, 256, False, 1),
+        'causal_odd':   (1, 1, 511, 32, True, 128, 128, 256, False, 2),
+        'short_flash':  (2, 1, 192, 32, False, 128, 128, 256, False, 3),
+        'causal_leaf':  (1, 2, 200, 32, True, 128, 128, 256, False, 4),
+        'smooth':       (1, 2, 512, 32, False, 256, 128, 256, True, 5),
+    }
+    for tag, (B, H, n, d, causal, bsz, ssz, msl, smooth, seed) in cases.items():
+        torch.manual_seed(seed)
+        q = torch.randn(B, H, n, d, requires_grad=True)
+        k = torch.randn(B, H, n, d, requires_grad=True)
+        v = torch.randn(B, H, n, d, requires_grad=True)
+        mod = RH.HyperAttention(input_dim=d, lsh_num_projs=8, block_size=bsz, sample_size=ssz, min_seq_len=msl,
+                                smooth_block=smooth)
+        mod.lsh.hash_triton = mod.lsh.hash_torch
+        try:
+            o, lse = mod(q, k, v, causal=causal, return_lse=True)
+        except Exception as e:  # a shape the reference itself cannot run is recorded as such
+            print('module', tag, 'reference raised', type(e).__name__, e)
+            torch.save({'raises': type(e).__name__}, os.path.join(out_dir, f'module_{tag}.pt'))
+            continue
+        do = torch.randn_like(o)
+        o.backward(do)
+        rec = {'q': q.detach(), 'k': k.detach(), 'v': v.detach(), 'proj_dir': mod.lsh.proj_dir.clone(), 'causal': causal,
+               'block_size': bsz, 'sample_size': ssz, 'min_seq_len': msl, 'smooth_block': smooth,
+               'o': o.detach().clone(), 'lse': lse.detach().clone(), 'do': do, 'dq': q.grad.clone(), 'dk': k.grad.clone(),
+               'dv': v.grad.clone()}
+        if tag == 'c0_noncausal':
+            # BASELINE config 0 in full.  Inputs are regenerated from the seed by the tests (q, k, v, then the
+            # module's proj_dir draw, then do, all from torch.manual_seed(seed)); big outputs keep every 8th row.
+            rec['q_codes'] = mod.lsh.hash_torch(q.detach()).to(torch.uint8)
+            rec['k_codes'] = mod.lsh.hash_torch(k.detach()).to(torch.uint8)
+            rec['q_sort_idx'] = torch.sort(rec['q_codes'].int(), dim=2, stable=True)[1].to(torch.int16)
+            rec['k_sort_idx'] = torch.sort(rec['k_codes'].int(), dim=2, stable=True)[1].to(torch.int16)
+            for name in ('q', 'k', 'v', 'do'):
+                rec.pop(name)
+            for name in ('o', 'dq', 'dk', 'dv'):
+                rec[name] = rec[name][:, :, ::8].clone()
+            rec['row_stride'] = 8
+            rec['seed'] = seed
+        torch.save(rec, os.path.join(out_dir, f'module_{tag}.pt'))
+        print('module', tag, 'o', tuple(o.shape), 'lse', tuple(lse.shape))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--reference', required=True)
+    ap.add_argument('--only', default='')
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    for name, fn in (('lsh', kernel_lsh), ('hyper', kernel_hyper), ('flash', kernel_flash), ('module', module_cases)):
+        if args.only and name not in args.only.split(','):
+            continue
+        fn(args.reference, HERE)
+
+
+if __name__ == '__main__':
+    main()
