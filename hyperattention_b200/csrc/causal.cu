@@ -1,0 +1,205 @@
+// Causal HyperAttention as one host-side schedule over the segment kernels.
+//
+// The reference recurses on the host: split the sequence in two, fold the halves into extra heads, recurse on the
+// diagonal blocks, run the un-masked kernel on the lower-left rectangle, merge, concatenate
+// (hyper_attention.py:51-96).  Unrolled, depth l (0 = top) holds 2^l spans of n/2^l rows per head; its rectangles
+// pair the second half of every span (queries) with the first half (keys), and the leaves at depth `levels` are
+// exact causal attention on spans of n/2^levels rows.  Here the whole tree is a flat list of launches on the
+// caller's [B,H,n,*] buffers: hash q and k once (a token's bucket does not depend on the depth), the leaves write
+// (o, lse), then the rectangles run deepest first and merge into the same rows in their epilogue -- the order in
+// which the reference's merges nest (stored value = attn1, rectangle = attn2).  No concatenation, no per-depth
+// copies.
+#include "attn_index.cuh"
+
+namespace ha {
+
+struct CausalPlan {
+  long long rows;          // B*H*n
+  long long idx_bytes;     // one depth's q_idx or k_idx
+  long long part_o_bytes, part_lse_bytes;
+  long long sort_ws;       // largest sort workspace over the depths
+  int leaf;
+};
+
+static int make_plan(const ha_causal_params& p, CausalPlan& pl) {
+  if (p.dtype != HA_BF16 && p.dtype != HA_FP16 && p.dtype != HA_FP32) return HA_ERR_DTYPE;
+  if (p.B <= 0 || p.H <= 0 || p.n <= 0 || p.d <= 0 || p.dv <= 0 || p.d > 256 || p.dv > 256) return HA_ERR_INVALID;
+  if (p.levels < 1 || p.levels > 24 || p.lsh_bits < 1 || p.lsh_bits > 16) return HA_ERR_INVALID;
+  if (p.n % (1 << p.levels) != 0) return HA_ERR_INVALID;
+  if (p.sample_size < 0 || p.sample_size % TILE != 0 || p.block_size < 1) return HA_ERR_INVALID;
+  pl.leaf = p.n >> p.levels;
+  // every rectangle must be a whole number of 128-row tiles and hold the sampled rows
+  if (pl.leaf % TILE != 0 || p.sample_size > pl.leaf) return HA_ERR_INVALID;
+  pl.rows = (long long)p.B * p.H * p.n;
+  pl.idx_bytes = pl.rows / 2 * 4;
+  pl.part_o_bytes = pl.rows * p.dv * dtype_size(p.dtype);
+  pl.part_lse_bytes = pl.rows * 4;
+  pl.sort_ws = 0;
+  for (int l = 0; l < p.levels; ++l) {
+    const int span = p.n >> l;
+    const long long ws = ha_seg_sort_workspace_bytes(p.B * p.H, p.n, span, span / 2, p.lsh_bits);
+    if (ws > pl.sort_ws) pl.sort_ws = ws;
+  }
+  return HA_OK;
+}
+
+static inline long long align256(long long x) { return (x + 255) / 256 * 256; }
+
+struct SavedLayout {
+  uint8_t* base;
+  CausalPlan pl;
+  int levels, keep_parts;
+  int32_t* q_idx(int l) const { return (int32_t*)(base + (long long)l * 2 * align256(pl.idx_bytes)); }
+  int32_t* k_idx(int l) const { return (int32_t*)(base + ((long long)l * 2 + 1) * align256(pl.idx_bytes)); }
+  long long parts_off() const { return (long long)levels * 2 * align256(pl.idx_bytes); }
+  // part index: 0..levels-1 = rectangles of that depth, levels = leaves
+  void* part_o(int part) const { return base + parts_off() + (long long)part * (align256(pl.part_o_bytes) + align256(pl.part_lse_bytes)); }
+  float* part_lse(int part) const { return (float*)((uint8_t*)part_o(part) + align256(pl.part_o_bytes)); }
+  long long total() const {
+    return parts_off() + (keep_parts ? (long long)(levels + 1) * (align256(pl.part_o_bytes) + align256(pl.part_lse_bytes)) : 0);
+  }
+};
+
+static void fill_attn(const ha_causal_params& p, ha_attn_params& a) {
+  a = ha_attn_params{};
+  a.dtype = p.dtype;
+  a.B = p.B; a.H = p.H; a.n = p.n; a.d = p.d; a.dv = p.dv;
+  a.block_size = p.block_size; a.sample_size = p.sample_size; a.scale = p.scale;
+  a.q = p.q; a.k = p.k; a.v = p.v;
+  a.q_sn = p.d; a.q_sh = (int64_t)p.n * p.d; a.q_sb = a.q_sh * p.H;
+  a.k_sn = p.d; a.k_sh = a.q_sh; a.k_sb = a.q_sb;
+  a.v_sn = p.dv; a.v_sh = (int64_t)p.n * p.dv; a.v_sb = a.v_sh * p.H;
+  a.o = p.o; a.o_sn = p.dv; a.o_sh = a.v_sh; a.o_sb = a.v_sb;
+  a.lse = p.lse;
+  a.d_o = p.d_o; a.do_sn = p.dv; a.do_sh = a.v_sh; a.do_sb = a.v_sb;
+  a.status = p.status;
+}
+
+}  // namespace ha
+
+using namespace ha;
+
+extern "C" {
+
+int64_t ha_causal_saved_bytes(const ha_causal_params* p) {
+  CausalPlan pl;
+  if (!p || make_plan(*p, pl) != HA_OK) return -1;
+  SavedLayout s{nullptr, pl, p->levels, p->keep_parts};
+  return s.total();
+}
+
+int64_t ha_causal_scratch_bytes(const ha_causal_params* p, int32_t backward) {
+  CausalPlan pl;
+  if (!p || make_plan(*p, pl) != HA_OK) return -1;
+  if (!backward) return 2 * align256(pl.rows * 4) + align256(pl.sort_ws);
+  return align256(pl.rows * p->d * 4) * 2 + align256(pl.rows * p->dv * 4) + align256(pl.rows * 4);
+}
+
+int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
+  if (!pp) return HA_ERR_INVALID;
+  const ha_causal_params& p = *pp;
+  CausalPlan pl;
+  int rc = make_plan(p, pl);
+  if (rc != HA_OK) return rc;
+  if (!p.q || !p.k || !p.v || !p.o || !p.lse || !p.proj) return HA_ERR_INVALID;
+  SavedLayout sv{(uint8_t*)p.saved, pl, p.levels, p.keep_parts};
+  if (!p.saved || p.saved_bytes < sv.total()) return HA_ERR_WORKSPACE;
+  if (!p.scratch || p.scratch_bytes < ha_causal_scratch_bytes(pp, 0)) return HA_ERR_WORKSPACE;
+  int32_t* codes_q = (int32_t*)p.scratch;
+  int32_t* codes_k = (int32_t*)((uint8_t*)p.scratch + align256(pl.rows * 4));
+  void* sort_ws = (uint8_t*)p.scratch + 2 * align256(pl.rows * 4);
+
+  const int64_t sn = p.d, sh = (int64_t)p.n * p.d, sb = sh * p.H;
+  rc = ha_lsh_hash(p.q, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes_q, stream);
+  if (rc != HA_OK) return rc;
+  rc = ha_lsh_hash(p.k, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes_k, stream);
+  if (rc != HA_OK) return rc;
+
+  ha_attn_params a;
+  fill_attn(p, a);
+  // leaves: exact causal attention on 2^levels spans per head
+  a.mode = HA_MODE_FLASH;
+  a.flags = HA_FLAG_CAUSAL | (p.flags & HA_FLAG_FORCE_SIMT);
+  a.segs_per_head = 1 << p.levels;
+  a.span = pl.leaf; a.q_off = 0; a.k_off = 0; a.m_q = pl.leaf; a.m_k = pl.leaf;
+  if (p.keep_parts) { a.part_o = sv.part_o(p.levels); a.part_lse = sv.part_lse(p.levels); }
+  rc = ha_attn_fwd(&a, stream);
+  if (rc != HA_OK) return rc;
+
+  for (int l = p.levels - 1; l >= 0; --l) {
+    const int span = p.n >> l, m = span / 2;
+    rc = ha_seg_sort(codes_q, p.B * p.H, p.n, span, m, m, p.lsh_bits, sv.q_idx(l), sort_ws, pl.sort_ws, stream);
+    if (rc != HA_OK) return rc;
+    rc = ha_seg_sort(codes_k, p.B * p.H, p.n, span, 0, m, p.lsh_bits, sv.k_idx(l), sort_ws, pl.sort_ws, stream);
+    if (rc != HA_OK) return rc;
+    a.mode = HA_MODE_HYPER;
+    a.flags = HA_FLAG_MERGE | (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_MERGE_EXACT | HA_FLAG_FORCE_SIMT));
+    a.segs_per_head = 1 << l;
+    a.span = span; a.q_off = m; a.k_off = 0; a.m_q = m; a.m_k = m;
+    a.q_idx = sv.q_idx(l); a.k_idx = sv.k_idx(l); a.sample_idx = nullptr;
+    if (p.keep_parts) { a.part_o = sv.part_o(l); a.part_lse = sv.part_lse(l); }
+    rc = ha_attn_fwd(&a, stream);
+    if (rc != HA_OK) return rc;
+  }
+  return HA_OK;
+}
+
+int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
+  if (!pp) return HA_ERR_INVALID;
+  const ha_causal_params& p = *pp;
+  CausalPlan pl;
+  int rc = make_plan(p, pl);
+  if (rc != HA_OK) return rc;
+  if (!p.q || !p.k || !p.v || !p.o || !p.lse || !p.d_o || !p.dq || !p.dk || !p.dv_out) return HA_ERR_INVALID;
+  SavedLayout sv{(uint8_t*)p.saved, pl, p.levels, p.keep_parts};
+  if (!p.saved || p.saved_bytes < sv.total()) return HA_ERR_WORKSPACE;
+  if (!p.scratch || p.scratch_bytes < ha_causal_scratch_bytes(pp, 1)) return HA_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* s = (uint8_t*)p.scratch;
+  float* dq_acc = (float*)s;                 s += align256(pl.rows * p.d * 4);
+  float* dk_acc = (float*)s;                 s += align256(pl.rows * p.d * 4);
+  float* dv_acc = (float*)s;                 s += align256(pl.rows * p.dv * 4);
+  float* delta = (float*)s;
+  HA_CUDA_OK(cudaMemsetAsync(dq_acc, 0, pl.rows * p.d * 4, st), "ha_causal_bwd memset");
+  HA_CUDA_OK(cudaMemsetAsync(dk_acc, 0, pl.rows * p.d * 4, st), "ha_causal_bwd memset");
+  HA_CUDA_OK(cudaMemsetAsync(dv_acc, 0, pl.rows * p.dv * 4, st), "ha_causal_bwd memset");
+
+  ha_attn_params a;
+  fill_attn(p, a);
+  a.delta = delta; a.dq_acc = dq_acc; a.dk_acc = dk_acc; a.dv_acc = dv_acc;
+  auto part_delta = [&](int part) -> int {
+    // reference gradient convention: every part uses sum(o_part * dO) of its own output (its d(lse) is dropped);
+    // exact convention: sum(o * dO) of the merged output, computed once
+    const void* o_src = p.keep_parts ? sv.part_o(part) : p.o;
+    return ha_delta(o_src, a.o_sb, a.o_sh, a.o_sn, p.d_o, a.do_sb, a.do_sh, a.do_sn, p.B, p.H, p.n, p.dv, p.dtype, delta, stream);
+  };
+  rc = part_delta(p.levels);
+  if (rc != HA_OK) return rc;
+  a.mode = HA_MODE_FLASH;
+  a.flags = HA_FLAG_CAUSAL | (p.flags & HA_FLAG_FORCE_SIMT);
+  a.segs_per_head = 1 << p.levels;
+  a.span = pl.leaf; a.q_off = 0; a.k_off = 0; a.m_q = pl.leaf; a.m_k = pl.leaf;
+  rc = ha_attn_bwd(&a, stream);
+  if (rc != HA_OK) return rc;
+  for (int l = p.levels - 1; l >= 0; --l) {
+    const int span = p.n >> l, m = span / 2;
+    if (p.keep_parts) {
+      rc = part_delta(l);
+      if (rc != HA_OK) return rc;
+    }
+    a.mode = HA_MODE_HYPER;
+    a.flags = p.flags & (HA_FLAG_SMOOTH | HA_FLAG_BWD_REF_SMOOTH | HA_FLAG_FORCE_SIMT);
+    a.segs_per_head = 1 << l;
+    a.span = span; a.q_off = m; a.k_off = 0; a.m_q = m; a.m_k = m;
+    a.q_idx = sv.q_idx(l); a.k_idx = sv.k_idx(l); a.sample_idx = nullptr;
+    rc = ha_attn_bwd(&a, stream);
+    if (rc != HA_OK) return rc;
+  }
+  rc = ha_cast_from_f32(dq_acc, p.dq, pl.rows * p.d, p.dtype, stream);
+  if (rc != HA_OK) return rc;
+  rc = ha_cast_from_f32(dk_acc, p.dk, pl.rows * p.d, p.dtype, stream);
+  if (rc != HA_OK) return rc;
+  return ha_cast_from_f32(dv_acc, p.dv_out, pl.rows * p.dv, p.dtype, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,178 @@
+"""The HyperAttention module: same constructor, attributes, forward signature and return values as the reference's
+torch.nn.Module (hyper_attention.py:9-132), computed by the sm_100a kernels of this package.
+
+Additional keyword arguments (all optional, accepted through **kwargs like the reference's unused kwargs):
+  grad_mode   'reference' (default): gradients follow the reference's conventions (d(lse) dropped by both attention
+              Functions, every merged part differentiated on its own); 'exact': gradient of the returned output.
+  merge_mode  'reference' (default): the merge of src/attn_utils.py:21-24 (weight rounded to the tensor dtype, eps
+              inside the log); 'exact': plain log-sum-exp combine.
+  rng         torch.Generator used to draw proj_dir (the reference's AngularLSHTriton has the same argument).
+  fused_causal  True (default): run regular causal shapes through the single-call schedule; False: always use the
+              per-level path built from the individual operators.
+"""
+import math
+
+import torch
+
+from . import _lib as L
+from . import ops
+
+
+class AngularLSH(torch.nn.Module):
+    """Sign-random-projection LSH with Gray-coded bucket ids; buffers and methods as AngularLSHTriton
+    (src/angular_lsh_triton.py:148-185): perm int32 [2^r], proj_dir [*dim, r], enc_vec int64 [1,1,1,r], all
+    non-persistent."""
+
+    def __init__(self, num_projs, dim, rng=None):
+        super().__init__()
+        self.num_projs = num_projs
+        if num_projs > 0:
+            b = torch.arange(2 ** num_projs, dtype=torch.int64)
+            self.register_buffer('perm', (b ^ (b >> 1)).to(torch.int32), persistent=False)
+            self.register_buffer('proj_dir', torch.randn(dim + (num_projs,), generator=rng), persistent=False)
+            self.register_buffer('enc_vec', 2 ** torch.arange(self.num_projs).view(1, 1, 1, -1), persistent=False)
+        else:
+            raise ValueError("Invalid value for num_projs")
+        self._proj_cache = None
+
+    def proj_f32(self):
+        """proj_dir as a contiguous float32 [d, r] tensor (values exactly those of the stored dtype)."""
+        pd = self.proj_dir
+        key = (pd.data_ptr(), pd._version, pd.dtype, pd.device)
+        if self._proj_cache is None or self._proj_cache[0] != key:
+            self._proj_cache = (key, pd.detach().reshape(pd.shape[-2], pd.shape[-1]).to(torch.float32).contiguous())
+        return self._proj_cache[1]
+
+    def hash_torch(self, mat):
+        """The reference's PyTorch formulation (src/angular_lsh_triton.py:175-179), kept for comparisons."""
+        mask = torch.einsum('...nd,...dr -> ...nr', mat, self.proj_dir)
+        mask = mask > 0
+        bin_ids = (mask * self.enc_vec).sum(-1)
+        return self.perm[bin_ids]
+
+    def hash_cuda(self, mat):
+        assert self.proj_dir.shape[:-2] == (1,) * (self.proj_dir.dim() - 2), 'one projection shared by all heads'
+        assert mat.dtype == self.proj_dir.dtype, 'All three tensors must have the same type'
+        return ops.lsh_hash(mat, self.proj_f32())
+
+    hash_triton = hash_cuda   # the name callers of the reference use
+
+    def __repr__(self):
+        return f"AngularLSH(num_proj={self.num_projs}, proj_dir.shape={self.proj_dir.shape})"
+
+
+class HyperAttention(torch.nn.Module):
+
+    def __init__(self, input_dim=64, lsh_num_projs=8, block_size=256, sample_size=256, min_seq_len=2048,
+                 smooth_block=False, **kwargs):
+        """block_size and sample_size must be divisible by 128 (as in the reference)."""
+        super().__init__()
+        self.input_dim = input_dim
+        self.lsh_num_projs = lsh_num_projs
+        self.block_size = block_size
+        self.sample_size = sample_size
+        self.min_seq_len = min_seq_len
+        self.smooth_block = smooth_block
+        self.grad_mode = kwargs.get('grad_mode', 'reference')
+        self.merge_mode = kwargs.get('merge_mode', 'reference')
+        self.fused_causal = kwargs.get('fused_causal', True)
+        self.kernel_flags = kwargs.get('kernel_flags', 0)
+        assert self.grad_mode in ('reference', 'exact') and self.merge_mode in ('reference', 'exact')
+        self.lsh = AngularLSH(num_projs=self.lsh_num_projs, dim=(1, 1, input_dim), rng=kwargs.get('rng'))
+
+    # ------------------------------------------------------------------------------------------
+    def _flags(self):
+        f = self.kernel_flags
+        if self.smooth_block:
+            f |= L.FLAG_SMOOTH
+            if self.grad_mode == 'reference':
+                f |= L.FLAG_BWD_REF_SMOOTH
+        if self.merge_mode == 'exact':
+            f |= L.FLAG_MERGE_EXACT
+        return f
+
+    def _causal_levels(self, n):
+        levels = 0
+        while (n >> levels) > self.min_seq_len and (n >> levels) % 2 == 0:
+            levels += 1
+        return levels
+
+    def _regular_causal(self, n):
+        """True when the single-call schedule applies: n halves evenly down to leaves <= min_seq_len and every
+        rectangle is a whole number of 128-row tiles that holds the sampled rows."""
+        levels = self._causal_levels(n)
+        leaf = n >> levels
+        return levels >= 1 and leaf <= self.min_seq_len and leaf % 128 == 0 and self.sample_size <= leaf \
+            and self.sample_size % 128 == 0
+
+    def forward(self, query: torch.tensor, key: torch.tensor, value: torch.tensor, scale=None, causal=False,
+                return_lse=False):
+        """query, key [B, H, n, d]; value [B, H, n, dv]; returns attn [B, H, n, dv] (and lse, float32 [B, H, n, 1];
+        [B, H, ceil(n/128)*128] when a causal call is short enough to be a single exact leaf, as in the reference)."""
+        query = query.contiguous()
+        key = key.contiguous()
+        value = value.contiguous()
+        n_query = query.shape[2]
+        batch_size, n_heads, n_key, dim = key.shape
+        scale = scale or dim ** (-0.5)
+        assert n_query == n_key
+
+        if causal is False:
+            attn, lse = self.forward_no_causal_mask(query, key, value, scale)
+        elif n_key <= self.min_seq_len:
+            attn, lse = ops.flash_attn_func(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), None, True,
+                                            scale, self.kernel_flags & L.FLAG_FORCE_SIMT)
+            attn = attn.transpose(1, 2)
+        elif self.fused_causal and self._regular_causal(n_key):
+            attn, lse = ops.CausalHyperFunc.apply(query, key, value, self.lsh.proj_f32(), self._causal_levels(n_key),
+                                                  self.block_size, self.sample_size, scale, self._flags(),
+                                                  self.grad_mode == 'reference')
+            lse = lse.unsqueeze(-1)
+        else:
+            attn, lse = self._causal_by_levels(query, key, value, scale)
+        if not return_lse:
+            return attn
+        return attn, lse
+
+    def _causal_by_levels(self, query, key, value, scale):
+        """One half-split built from the individual operators (any shape the reference accepts, including the
+        zero-row padding of odd lengths, hyper_attention.py:59-96); recurses through forward()."""
+        B, H, n, dim = key.shape
+        odd = n % 2
+        if odd:
+            query, key, value = [torch.nn.functional.pad(t, (0, 0, 0, 1)) for t in (query, key, value)]
+        m = query.shape[2] // 2
+        halves = lambda t: t.reshape(B, 2 * H, m, t.shape[-1])
+        attn_d, lse_d = self.forward(halves(query), halves(key), halves(value), scale, True, True)
+        attn_d = attn_d.reshape(B, H, 2 * m, -1)
+        lse_d = lse_d.reshape(B, H, 2 * m, 1)          # fails like the reference when a leaf is not 128-aligned
+        attn_r, lse_r = self.forward_no_causal_mask(query[:, :, m:], key[:, :, :m], value[:, :, :m], scale)
+        if self.merge_mode == 'exact':
+            mx = torch.maximum(lse_d[:, :, m:], lse_r)
+            w1, w2 = (lse_d[:, :, m:] - mx).exp(), (lse_r - mx).exp()
+            low = ((attn_d[:, :, m:] * w1 + attn_r * w2) / (w1 + w2)).to(attn_r.dtype)
+            lse_low = mx + (w1 + w2).log()
+        else:
+            low, lse_low = ops.add_self_attentions(attn_d[:, :, m:], lse_d[:, :, m:], attn_r, lse_r)
+        attn = torch.cat((attn_d[:, :, :m], low), dim=-2)
+        lse = torch.cat((lse_d[:, :, :m], lse_low), dim=-2)
+        if odd:
+            attn, lse = attn[:, :, :-1], lse[:, :, :-1]
+        return attn, lse
+
+    def forward_no_causal_mask(self, query, key, value, scale):
+        """hyper_attention.py:103-132: exact attention below min_seq_len, otherwise hash -> stable sort -> fused
+        block-diagonal + sampled attention."""
+        B, H, n_query, dim = query.shape
+        if self.min_seq_len > n_query:
+            attn, lse = ops.flash_attn_func(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), None, False,
+                                            scale, self.kernel_flags & L.FLAG_FORCE_SIMT)
+        else:
+            bits = self.lsh_num_projs
+            q_idx = ops.seg_sort(self.lsh.hash_cuda(query), bits).view(B, H, n_query)
+            k_idx = ops.seg_sort(self.lsh.hash_cuda(key), bits).view(B, H, key.shape[2])
+            attn, lse = ops.hyper_attn_func(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2),
+                                            q_idx.transpose(1, 2), k_idx.transpose(1, 2), self.block_size, self.sample_size,
+                                            scale, self.smooth_block, None, self._flags() & ~L.FLAG_SMOOTH)
+        attn = attn.transpose(1, 2)
+        return attn, lse.unsqueeze(-1)
