@@ -5,8 +5,9 @@ namespace ha {
 int simt_attn_fwd(const ha_attn_params& p, cudaStream_t st);
 int simt_attn_bwd(const ha_attn_params& p, cudaStream_t st);
 int tc_attn_fwd(const ha_attn_params& p, cudaStream_t st);
-int tc_attn_bwd(const ha_attn_params& p, cudaStream_t st);
 bool tc_supported(const ha_attn_params& p);
+bool tc_bwd_supported(const ha_attn_params& p);
+int tc_attn_bwd(const ha_attn_params& p, cudaStream_t st);
 
 static int check_common(const ha_attn_params& p, bool backward) {
   if (p.dtype != HA_BF16 && p.dtype != HA_FP16 && p.dtype != HA_FP32) return HA_ERR_DTYPE;
@@ -55,7 +56,7 @@ int ha_attn_bwd(const ha_attn_params* p, void* stream) {
   int rc = check_common(*p, true);
   if (rc != HA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  if (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_supported(*p)) return tc_attn_bwd(*p, st);
+  if (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(*p)) return tc_attn_bwd(*p, st);
   return simt_attn_bwd(*p, st);
 }
 

@@ -298,7 +298,9 @@ int64_t ha_launch_count(void) { return (int64_t)g_launches.load(); }
 
 int ha_lsh_hash(const void* x, int64_t sb, int64_t sh, int64_t sn, int32_t B, int32_t H, int32_t n, int32_t d, int32_t dtype,
                 const float* proj, int32_t r, int32_t* codes, void* stream) {
-  if (!x || !proj || !codes || B < 0 || H < 0 || n < 0 || d <= 0 || d > 256 || r < 1 || r > 16) return HA_ERR_INVALID;
+  if (B < 0 || H < 0 || n < 0 || d <= 0 || d > 256 || r < 1 || r > 16) return HA_ERR_INVALID;
+  if ((long long)B * H * n == 0) return HA_OK;
+  if (!x || !proj || !codes) return HA_ERR_INVALID;
   cudaStream_t st = (cudaStream_t)stream;
   switch (dtype) {
     case HA_BF16: return launch_hash<__nv_bfloat16>(x, sb, sh, sn, B, H, n, d, proj, r, codes, st);

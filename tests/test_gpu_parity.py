@@ -46,10 +46,10 @@ def test_lsh_codes_bit_exact(ha, dtype, shape, r):
     proj = torch.randn(1, 1, shape[-1], r).to(dtype)
     codes = ha.lsh_hash(dev(x), dev(proj.float().view(shape[-1], r).contiguous())).cpu()
     want = O.lsh_hash(x, proj)
-    ties = O.lsh_tie_mask(x, proj, rel=2.0 ** -16)
+    ties = O.lsh_tie_mask(x, proj, rel=2.0 ** -18)
     assert codes.dtype == torch.int32 and codes.shape == x.shape[:-1]
     assert not ((codes != want) & ~ties).any()
-    assert ties.float().mean() < 1e-3 or x.numel() == 0
+    assert x.numel() == 0 or ties.float().mean() < 2e-3
 
 
 def test_lsh_strided_input_and_module_buffers(ha):
@@ -59,7 +59,7 @@ def test_lsh_strided_input_and_module_buffers(ha):
     x = torch.randn(2, 200, 3, 64, device='cuda').to(torch.bfloat16).transpose(1, 2)   # [B,H,n,d] view, strided
     codes = lsh.hash_triton(x)
     want = O.lsh_hash(x.cpu(), lsh.proj_dir.cpu())
-    ties = O.lsh_tie_mask(x.cpu(), lsh.proj_dir.cpu(), rel=2.0 ** -16)
+    ties = O.lsh_tie_mask(x.cpu(), lsh.proj_dir.cpu(), rel=2.0 ** -18)
     assert not ((codes.cpu() != want) & ~ties).any()
     assert torch.equal(lsh.perm.cpu(), O.gray_table(8))
 
@@ -69,7 +69,7 @@ def test_lsh_golden_reference_kernel(ha, golden_dir, tag):
     r = torch.load(os.path.join(golden_dir, f'kernel_lsh_{tag}.pt'))
     d, nb = r['proj_dir'].shape[-2:]
     codes = ha.lsh_hash(dev(r['x']), dev(r['proj_dir'].float().view(d, nb).contiguous())).cpu()
-    ties = O.lsh_tie_mask(r['x'], r['proj_dir'], rel=2.0 ** -16)
+    ties = O.lsh_tie_mask(r['x'], r['proj_dir'], rel=2.0 ** -18)
     assert not ((codes != r['codes_kernel']) & ~ties).any()
 
 
