@@ -1,0 +1,321 @@
+"""Benchmark of the HyperAttention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2] [--impl reference] [--seq-len n] [--heads H]
+
+A step is one forward+backward pass of the HyperAttention module over one synthetic batch of the headline shape
+(batch 1, 32 heads, head_dim 64, 131072 tokens, bf16; BASELINE config 1 = non-causal, config 2 = causal).  The
+heads are partitioned over the GPUs (no collective on the data path); the time of a step is the maximum over ranks,
+measured with CUDA events.  One JSON line is printed by rank 0.
+
+--impl reference times the CPU restatement of the reference (the oracle) on the host cores on a bounded sample of
+the same workload (a subset of heads), as the reference's own attention kernels cannot run on a CPU.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch
+
+HEADS, DIM, SEQ = 32, 64, 131072
+BLOCK, SAMPLE, MIN_SEQ, BITS = 256, 256, 2048, 8
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
+    ap.add_argument('--workload', default='c1', choices=['c1', 'c2'])
+    ap.add_argument('--seq-len', type=int, default=SEQ)
+    ap.add_argument('--heads', type=int, default=HEADS)
+    ap.add_argument('--no-extras', action='store_true', help='skip the exact-flash comparator, cpu baseline and per-kernel roofline legs')
+    ap.add_argument('--cpu-heads', type=int, default=1, help='heads in the CPU-baseline sample')
+    return ap.parse_args()
+
+
+def clustered_inputs(heads, n, d, seed, device='cpu', dtype=torch.bfloat16):
+    """BASELINE configs 1/2: per head 64 unit-norm centroids shared by Q and K, per-token Gaussian noise of total norm
+    ~0.3, V ~ N(0,1), dO ~ N(0,1).  Seeded, generated on the CPU generator so that every rank/impl sees the same data."""
+    g = torch.Generator().manual_seed(seed)
+    cent = torch.randn(heads, 64, d, generator=g)
+    cent = cent / cent.norm(dim=-1, keepdim=True)
+    def draw():
+        a = torch.randint(0, 64, (heads, n), generator=g)
+        x = torch.gather(cent, 1, a.unsqueeze(-1).expand(-1, -1, d))
+        return x + torch.randn(heads, n, d, generator=g) * (0.3 / math.sqrt(d))
+    q = draw().unsqueeze(0)
+    k = draw().unsqueeze(0)
+    v = torch.randn(1, heads, n, d, generator=g)
+    do = torch.randn(1, heads, n, d, generator=g)
+    return [t.to(dtype).to(device) for t in (q, k, v, do)]
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = 'index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,' \
+        'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap'
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.idx), f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
+                                          '-lms', '200'], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(',')]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), f[4:8]):
+                if val.lower().startswith('active'):
+                    reasons.add(name)
+        sm.sort()
+        return {'sm_mhz': sm[len(sm) // 2] if sm else None, 'sm_max_mhz': mx, 'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+def timed(fn, steps, warmup, sync_all):
+    """warmup untimed calls, then `steps` calls between CUDA events on the current stream; returns ms per step."""
+    for _ in range(warmup):
+        fn()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    e1.synchronize()
+    sync_all()
+    return e0.elapsed_time(e1) / steps
+
+
+def cpu_baseline(workload, n, d, heads_sample, total_heads, seed):
+    """The reference's host-side path restated on the CPU (oracle): its glue, hash, stable sort and merge, with the two
+    device-only attention callables replaced by the oracle's PyTorch Functions.  Timed on `heads_sample` heads and
+    scaled linearly to `total_heads`."""
+    from oracle import hyper_oracle as O
+    q, k, v, do = clustered_inputs(heads_sample, n, d, seed, dtype=torch.float32)
+    g = torch.Generator().manual_seed(1234)
+    proj = torch.randn(1, 1, d, BITS, generator=g)
+    orc = O.HyperAttentionOracle(proj, BLOCK, SAMPLE, MIN_SEQ, False)
+    q, k, v = [t.requires_grad_() for t in (q, k, v)]
+    t0 = time.perf_counter()
+    o = orc(q, k, v, causal=(workload == 'c2'))
+    t1 = time.perf_counter()
+    o.backward(do)
+    t2 = time.perf_counter()
+    scale = total_heads / heads_sample
+    sec = (t2 - t0) * scale
+    return {'value': n / sec, 'unit': 'tokens/s', 'cores': torch.get_num_threads(), 'kind': 'port',
+            'sample': f'{heads_sample} of {total_heads} heads at n={n}, fp32, fwd {t1 - t0:.2f}s + bwd {t2 - t1:.2f}s, scaled x{scale:g} '
+                      f'(reference glue/hash/sort/merge restated in PyTorch; attention kernels restated because the '
+                      f'reference has none for CPU)',
+            'host_cpus': os.cpu_count(), 'fwd_s_scaled': (t1 - t0) * scale, 'fwd_bwd_s_scaled': sec}
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get('RANK', 0))
+    world = int(os.environ.get('WORLD_SIZE', 1))
+    local_rank = int(os.environ.get('LOCAL_RANK', 0))
+    n, d, heads = args.seq_len, DIM, args.heads
+    causal = args.workload == 'c2'
+    seed = 1 if args.workload == 'c1' else 2
+    config = {'workload': f"BASELINE config {'2 (causal)' if causal else '1 (non-causal)'}: batch 1, {heads} heads, head_dim {d}, "
+                          f"seq_len {n}, bf16, block 256, sample 256, lsh 8 bits" + (', min_seq_len 2048' if causal else ''),
+              'step': 'forward + backward of HyperAttention.forward', 'heads_per_gpu': heads // max(world, 1),
+              'partition': 'heads over GPUs, no collective', 'l2': 'inputs (4 x 537 MB per step at 1 GPU) exceed the 126 MB L2',
+              'grad_mode': 'reference'}
+
+    if args.impl == 'reference':
+        if rank != 0:
+            return
+        cb = cpu_baseline(args.workload, n, d, args.cpu_heads, heads, seed)
+        vals = [cb['value']]
+        for _ in range(max(0, args.steps - 1)):
+            vals.append(cpu_baseline(args.workload, n, d, args.cpu_heads, heads, seed)['value'])
+        val = sum(vals) / len(vals)
+        cb['value'] = val
+        line = {'impl': 'reference', 'metric': 'hyperattention_fwd_bwd_tokens_per_s', 'value': val, 'unit': 'tokens/s', 'n_gpus': args.gpus,
+                'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 * n / val, 'higher_is_better': True, 'scaling': 'strong',
+                'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic', 'config': config, 'cpu_baseline': cb,
+                'e2e': {'value': val, 'unit': 'tokens/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}
+        print(json.dumps(line))
+        return
+
+    assert torch.cuda.is_available(), 'bench.py needs a CUDA device'
+    import hyperattention_b200 as ha
+    torch.cuda.set_device(local_rank)
+    dev = torch.device('cuda', local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group('nccl', device_id=dev)
+    assert heads % world == 0
+    hpg = heads // world
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # same data on every world size: generate all heads on the host, keep this rank's slice
+    host = clustered_inputs(heads, n, d, seed)
+    host = [t[:, rank * hpg:(rank + 1) * hpg].contiguous().pin_memory() for t in host]
+    q, k, v, do = [t.to(dev) for t in host]
+    q, k, v = [t.requires_grad_() for t in (q, k, v)]
+    gen = torch.Generator().manual_seed(1234)
+    mod = ha.HyperAttention(input_dim=d, lsh_num_projs=BITS, block_size=BLOCK, sample_size=SAMPLE, min_seq_len=MIN_SEQ,
+                            rng=gen).to(device=dev, dtype=torch.bfloat16)
+
+    def fwd():
+        with torch.no_grad():
+            return mod(q, k, v, causal=causal)
+
+    def fwd_bwd():
+        o = mod(q, k, v, causal=causal)
+        return torch.autograd.grad(o, (q, k, v), do)
+
+    sampler = ClockSampler(torch.cuda.current_device() if 'CUDA_VISIBLE_DEVICES' not in os.environ else local_rank)
+    launches0 = ha.launch_count()
+    fwd_bwd()   # first call: allocator growth
+    sync_all()
+    sampler.start()
+    l0 = ha.launch_count()
+    ms = timed(fwd_bwd, args.steps, args.warmup, sync_all)
+    launches = (ha.launch_count() - l0) // (args.steps + args.warmup) * args.steps
+    clocks = sampler.stop()
+    ms_fwd = timed(fwd, args.steps, args.warmup, sync_all)
+    if dist is not None:
+        t = torch.tensor([ms, ms_fwd], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, ms_fwd = t.tolist()
+
+    # end to end through the public API with host buffers: pinned H2D of q, k, v, do; D2H of o and the three gradients
+    outs = [torch.empty_like(t) for t in host]
+    def e2e_step():
+        qd, kd, vd, dod = [t.to(dev, non_blocking=True) for t in host]
+        qd, kd, vd = [t.requires_grad_() for t in (qd, kd, vd)]
+        o = mod(qd, kd, vd, causal=causal)
+        grads = torch.autograd.grad(o, (qd, kd, vd), dod)
+        for dst, src in zip(outs, (o.detach(),) + grads):
+            dst.copy_(src, non_blocking=True)
+    ms_e2e = timed(e2e_step, max(2, args.steps // 2), 2, sync_all)
+    if dist is not None:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = t.item()
+    bytes_io = sum(t.numel() * t.element_size() for t in host)
+
+    line = {'metric': 'hyperattention_fwd_bwd_tokens_per_s', 'value': n / (ms * 1e-3), 'unit': 'tokens/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong',
+            'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic', 'config': config, 'fwd_ms': ms_fwd, 'fwd_tokens_per_s': n / (ms_fwd * 1e-3),
+            'clocks': clocks, 'gpu_launches': int(launches),
+            'e2e': {'value': n / (ms_e2e * 1e-3), 'unit': 'tokens/s', 'ms_per_step': ms_e2e, 'h2d_bytes_per_step': bytes_io,
+                    'd2h_bytes_per_step': bytes_io}}
+
+    if rank == 0 and not args.no_extras:
+        line.update(extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev))
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
+    """roofline of the dominant kernel (timed alone, CUDA events), the exact-flash comparator, the CPU baseline."""
+    from hyperattention_b200 import ops
+    peaks = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'src': 'fallback'}
+    pk = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(pk):
+        m = json.load(open(pk))
+        peaks = {'hbm_gbs': m['hbm_gbs'], 'bf16_tflops': m['bf16_tflops'], 'src': 'measured'}
+    sync = torch.cuda.synchronize
+    out = {}
+    rows = hpg * n
+    with torch.no_grad():
+        qd, kd, vd = q.detach(), k.detach(), v.detach()
+        proj = mod.lsh.proj_f32()
+        # stage timings of one non-causal call over this rank's heads
+        t_hash = timed(lambda: ops.lsh_hash(qd, proj), 10, 3, sync)
+        codes = ops.lsh_hash(qd, proj)
+        t_sort = timed(lambda: ops.seg_sort(codes, BITS), 10, 3, sync)
+        qi = ops.seg_sort(codes, BITS).view(1, hpg, n)
+        ki = ops.seg_sort(ops.lsh_hash(kd, proj), BITS).view(1, hpg, n)
+        T = lambda t: t.transpose(1, 2)
+        t_attn = timed(lambda: ops.hyper_attn_func(T(qd), T(kd), T(vd), T(qi), T(ki), BLOCK, SAMPLE), 10, 3, sync)
+        flops = 4.0 * (BLOCK + SAMPLE) * d * rows
+        out['stages_ms'] = {'lsh_hash_per_tensor': t_hash, 'seg_sort_per_tensor': t_sort, 'hyper_attn_fwd': t_attn}
+        out['stage_rooflines'] = {
+            'lsh_hash': {'bound': 'hbm', 'achieved': rows * (d * 2 + 4) / t_hash / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
+            'seg_sort': {'bound': 'hbm', 'achieved': rows * 8 / t_sort / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
+            'hyper_attn_fwd_hbm': {'bound': 'hbm', 'achieved': rows * (4 * d * 2 + 12) / t_attn / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
+        }
+        for r_ in out['stage_rooflines'].values():
+            r_['frac'] = r_['achieved'] / r_['peak']
+        ach = flops / (t_attn * 1e-3) / 1e12
+        out['roofline'] = {'bound': 'tensor', 'kernel': 'attn_tc_fwd_kernel (hyper pattern, forward)', 'achieved': ach,
+                           'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s', 'frac': ach / peaks['bf16_tflops'], 'traffic': None,
+                           'peak_source': peaks['src'], 'launch_ms': t_attn,
+                           'algorithmic_flops_per_launch': flops}
+        # exact attention of the same shape: our sm_100a flash kernel and the library kernel behind torch SDPA
+        t_ours = timed(lambda: ops.flash_attn_func(T(qd), T(kd), T(vd), None, True), 2, 1, sync)
+        out['exact_flash'] = {'ours_causal_fwd_ms': t_ours, 'ours_causal_fwd_tflops': 2.0 * n * n * d * hpg / (t_ours * 1e-3) / 1e12}
+    try:
+        import torch.nn.functional as F
+        qs, ks, vs = [t.detach().clone().requires_grad_() for t in (q, k, v)]
+        f = lambda: F.scaled_dot_product_attention(qs, ks, vs, is_causal=True)
+        t_f = timed(lambda: f(), 2, 1, sync)
+        def fb():
+            o = f()
+            torch.autograd.grad(o, (qs, ks, vs), do)
+        t_fb = timed(fb, 2, 1, sync)
+        out['exact_flash'].update({'sdpa_causal_fwd_ms': t_f, 'sdpa_causal_fwd_bwd_ms': t_fb})
+        del qs, ks, vs
+    except Exception as e:   # the comparator is informative only
+        out['exact_flash']['sdpa_error'] = str(e)[:200]
+    try:
+        out['cpu_baseline'] = cpu_baseline(args.workload, n, d, args.cpu_heads, heads, seed)
+    except Exception as e:
+        out['cpu_baseline'] = {'error': str(e)[:200]}
+    return out
+
+
+if __name__ == '__main__':
+    main()
