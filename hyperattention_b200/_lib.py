@@ -15,7 +15,8 @@ MODE_HYPER, MODE_FLASH = 0, 1
 FLAG_CAUSAL, FLAG_SMOOTH, FLAG_MERGE, FLAG_MERGE_EXACT, FLAG_BWD_REF_SMOOTH, FLAG_FORCE_SIMT = 1, 2, 4, 8, 16, 32
 
 _STATUS = {-1: 'invalid argument (shape / stride / size not accepted)', -2: 'unsupported dtype',
-           -3: 'workspace missing or too small', -4: 'CUDA runtime error', 1: 'device-side wait timed out'}
+           -3: 'workspace missing or too small', -4: 'CUDA runtime error', 1: 'device-side wait timed out',
+           -5: 'needs more scratch than the library\'s built-in array holds (use the entry point that takes a workspace)'}
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
@@ -58,6 +59,7 @@ SIGNATURES = {
     'ha_lsh_hash': (C.c_int, [vp, i64, i64, i64, i32, i32, i32, i32, i32, vp, i32, vp, vp]),
     'ha_seg_sort_workspace_bytes': (i64, [i32, i32, i32, i32, i32]),
     'ha_seg_sort': (C.c_int, [vp, i32, i32, i32, i32, i32, i32, vp, vp, i64, vp]),
+    'ha_seg_sort_noalloc': (C.c_int, [vp, i32, i32, i32, i32, i32, i32, vp, vp]),
     'ha_gather_rows': (C.c_int, [vp, i64, i64, i64, i32, i32, i32, i32, vp, i32, vp, vp]),
     'ha_attn_fwd': (C.c_int, [C.POINTER(AttnParams), vp]),
     'ha_attn_bwd': (C.c_int, [C.POINTER(AttnParams), vp]),

@@ -10,6 +10,8 @@
 // Traffic per digit pass: keys read twice (4 B each) + one 4 B index written, plus 1 KB of counters per sub-chunk.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace ha {
 
 constexpr int SUB = 1024;          // keys per warp
@@ -156,3 +158,50 @@ int ha_seg_sort(const int32_t* codes, int32_t rows, int32_t n, int32_t span, int
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of ha_seg_sort.
+//
+// Some hosts of this library are not in a position to hand over a workspace: an inference server that has already
+// given all of HBM to its own pools, a plug-in loaded without any allocator of its own (no torch, no cudaMalloc
+// rights inside a captured or latency-critical region, where cudaMalloc would also synchronise the device).  For
+// them the counters (and, for keys wider than 8 bits, the intermediate permutation) live in a fixed array that is
+// part of the library image, HA_SEG_SORT_STATIC_BYTES bytes on every GPU that loads the library, until exit.
+//
+// g_sort_scratch names device memory only in device code.  On the host the identifier is a handle, not an address a
+// kernel may be given; the address is looked up once per device with cudaGetSymbolAddress while that device is
+// current, and that pointer is what the kernels receive.
+// ---------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_sort_scratch[HA_SEG_SORT_STATIC_BYTES];
+
+namespace ha {
+constexpr int MAX_DEVICES = 64;
+static std::mutex g_scratch_mu;
+static void* g_scratch_ptr[MAX_DEVICES] = {nullptr};
+}  // namespace ha
+
+extern "C" int ha_seg_sort_noalloc(const int32_t* codes, int32_t rows, int32_t n, int32_t span, int32_t seg_off, int32_t seg_len,
+                                   int32_t key_bits, int32_t* idx_out, void* stream) {
+  if (rows < 0 || n < 0 || span <= 0 || seg_len < 0 || seg_off < 0 || key_bits < 1 || key_bits > 16) return HA_ERR_INVALID;
+  if (n % span != 0 || seg_off + seg_len > span) return HA_ERR_INVALID;
+  if (rows == 0 || n == 0 || seg_len == 0) return HA_OK;
+  if (ha_seg_sort_workspace_bytes(rows, n, span, seg_len, key_bits) > (int64_t)HA_SEG_SORT_STATIC_BYTES) return HA_ERR_TOO_LARGE;
+  int dev = -1;
+  HA_CUDA_OK(cudaGetDevice(&dev), "ha_seg_sort_noalloc cudaGetDevice");
+  if (dev < 0 || dev >= ha::MAX_DEVICES) return HA_ERR_INVALID;
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(ha::g_scratch_mu);
+    if (!ha::g_scratch_ptr[dev]) {
+      void* ptr = nullptr;
+      HA_CUDA_OK(cudaGetSymbolAddress(&ptr, g_sort_scratch), "ha_seg_sort_noalloc cudaGetSymbolAddress");
+      if (!ptr) return HA_ERR_CUDA;
+      ha::g_scratch_ptr[dev] = ptr;
+    }
+    scratch = ha::g_scratch_ptr[dev];
+  }
+  // Nothing in the array has to start at zero: every counter block and every intermediate index a pass reads is
+  // written by that same call first, so the previous call's contents are simply overwritten.
+  return ha_seg_sort(codes, rows, n, span, seg_off, seg_len, key_bits, idx_out, scratch, (int64_t)HA_SEG_SORT_STATIC_BYTES, stream);
+}
+

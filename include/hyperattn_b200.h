@@ -24,7 +24,8 @@ enum {
   HA_ERR_DTYPE = -2,        /* unsupported element type */
   HA_ERR_WORKSPACE = -3,    /* workspace pointer null or too small */
   HA_ERR_CUDA = -4,         /* a CUDA runtime call (launch, attribute) failed; see ha_last_cuda_error */
-  HA_DEV_TIMEOUT = 1        /* a bounded device-side wait gave up (read back through ha_read_status) */
+  HA_ERR_TOO_LARGE = -5,    /* ha_seg_sort_noalloc: the sort needs more scratch than the built-in array holds */
+  HA_DEV_TIMEOUT = 1        /* a bounded device-side wait gave up (written to the caller's status word) */
 };
 
 enum { HA_BF16 = 0, HA_FP16 = 1, HA_FP32 = 2 };
@@ -69,6 +70,25 @@ int ha_lsh_hash(const void* x, int64_t stride_b, int64_t stride_h, int64_t strid
 int64_t ha_seg_sort_workspace_bytes(int32_t rows, int32_t n, int32_t span, int32_t seg_len, int32_t key_bits);
 int ha_seg_sort(const int32_t* codes, int32_t rows, int32_t n, int32_t span, int32_t seg_off, int32_t seg_len,
                 int32_t key_bits, int32_t* idx_out, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* The same sort for callers that have no memory to give: embedders that cannot call cudaMalloc themselves (all of
+ * device memory already belongs to their own pools, or they sit in a region where an allocation -- and the device-wide
+ * synchronisation it implies -- is not allowed) and do not link an allocator such as torch's.  The scratch is a fixed
+ * array of HA_SEG_SORT_STATIC_BYTES inside the library image, resident on every GPU that loads the library until the
+ * process exits.  This entry point has no counterpart in the reference; it exists only for such embedders.
+ *   - Inputs and the output are still the caller's.  No cudaMalloc, cudaFree or other allocating routine is called.
+ *   - A sort that would need more than HA_SEG_SORT_STATIC_BYTES of scratch (ha_seg_sort_workspace_bytes tells) is
+ *     refused with HA_ERR_TOO_LARGE and nothing is launched.  With 8-bit keys that is 4096 sub-chunks of 1024 keys,
+ *     e.g. 32 heads x 131072 tokens.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call before any stream capture begins.
+ *   - All calls on a device share the one array and find in it whatever the previous call left; nothing in it needs
+ *     clearing, because each call writes every word before reading it.  Two calls that overlap on the GPU (different
+ *     streams, or different host threads) race on it: serialise them.
+ */
+#define HA_SEG_SORT_STATIC_BYTES (4u << 20)
+int ha_seg_sort_noalloc(const int32_t* codes, int32_t rows, int32_t n, int32_t span, int32_t seg_off, int32_t seg_len,
+                        int32_t key_bits, int32_t* idx_out, void* stream);
 
 /* --------------------------------------------------------------------------------------------------------------
  * Row gather: dst[g, i, :] = src[head(g), base(g) + idx[g, i], :].  Replaces indexing()
