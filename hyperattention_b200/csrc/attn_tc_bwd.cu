@@ -1,7 +1,8 @@
 // Attention backward on tcgen05 tensor cores + TMEM, bf16/fp16, head dims 64 and 128.
 //
-// One CTA of 128 threads owns one tile of 128 keys and walks the query tiles that pair with it.  Per (key tile,
-// query tile) pair, with thread i = TMEM lane i:
+// One CTA of 256 threads (two groups of 128; thread (g, i) = TMEM lane i, the groups split the columns of the
+// elementwise phase and of the reductions) owns one tile of 128 keys and walks the query tiles that pair with it.
+// Per (key tile, query tile) pair:
 //   S  = Q K^T    (lanes = queries)      dP = dO V^T   (lanes = queries)            -> TMEM, fp32
 //   p  = exp2(S*scale*log2e - lse*log2e),  ds = p * (dP - delta) * scale            per thread: its query row
 //   P and dS are rounded to the input dtype and written to shared memory as [query][key] swizzled tiles, which serve
@@ -9,7 +10,7 @@
 //   dV += P^T dO  (lanes = keys, accumulates in TMEM over the query tiles)
 //   dK += dS^T Q  (lanes = keys, accumulates in TMEM)
 //   dQ  = dS K    (lanes = queries) -> staged through shared memory -> coalesced fp32 vector reductions into dq_acc
-// At the end the key tile's dK/dV rows are reduced into dk_acc/dv_acc (fp32, vector reductions).
+// At the end the key tile's dK/dV rows are reduced into dk_acc/dv_acc the same way.
 //
 // Work items of a segment: hyper = one item per sorted key tile (block window of query tiles through q_idx), plus
 // (sampled key tile x chunk of query tiles in natural order) items; flash = (key tile x chunk of query tiles) with the
@@ -21,10 +22,16 @@
 
 namespace ha {
 
-constexpr int BWD_CHUNK = 4;   // query tiles per sampled / flash work item
+constexpr int BWD_CHUNK = 16;  // query tiles per sampled / flash work item
+
+// bytes of one column half of a reduction staging tile (128 rows x NC floats)
+template <int NC> struct RedStage { static constexpr int BYTES = TILE * NC * 4; };
 
 template <int D, int DV> struct BwdCfg {
-  static constexpr int STAGES = (D == 64 && DV == 64) ? 2 : 1;
+  // PIPE (head dims 64): query tiles double buffered, dQ double buffered in its own TMEM columns and a separate staging
+  // tile, so that the MMAs of pair j and the S/dP MMAs of pair j+1 run as one batch underneath the thread work.
+  static constexpr bool PIPE = (D == 64 && DV == 64);
+  static constexpr int STAGES = PIPE ? 2 : 1;
   static constexpr int K_BYTES = TILE * D * 2, V_BYTES = TILE * DV * 2;
   static constexpr int Q_BYTES = TILE * D * 2, DO_BYTES = TILE * DV * 2;
   static constexpr int P_BYTES = TILE * TILE * 2;
@@ -34,8 +41,14 @@ template <int D, int DV> struct BwdCfg {
   static constexpr int OFF_DO = OFF_Q + STAGES * Q_BYTES;
   static constexpr int OFF_P = OFF_DO + STAGES * DO_BYTES;
   static constexpr int OFF_DS = OFF_P + P_BYTES;
-  static constexpr int SMEM = OFF_DS + P_BYTES + 1024;
-  static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = 384, COL_DQ = 0;
+  // staging rows of the reductions (two column halves): a tile of its own when pipelined, else over the idle
+  // P / dS tiles (which it may outgrow by a few KB)
+  static constexpr int MAXD = D > DV ? D : DV;
+  static constexpr int STG_HALF = RedStage<MAXD / 2>::BYTES;
+  static constexpr int OFF_STG = PIPE ? OFF_DS + P_BYTES : OFF_P;
+  static constexpr int SMEM = (OFF_STG + 2 * STG_HALF > OFF_DS + P_BYTES ? OFF_STG + 2 * STG_HALF : OFF_DS + P_BYTES) + 1024;
+  // TMEM columns: S [0,128), dP [128,256), dV [256,256+DV), dK; dQ: two buffers of its own (PIPE) or over S
+  static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = PIPE ? 320 : 384, COL_DQ = PIPE ? 384 : 0;
 };
 
 template <int COLS>
@@ -60,43 +73,98 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-// fp32 rows held one per thread (n_cols values in TMEM order) -> staged in shared memory -> reduced into global rows
-// by index with 16-byte vector reductions, 16 lanes per 64-float slice so that a warp instruction covers two rows.
-template <int NCOLS>
+// NC fp32 values per thread (columns [0, NC) at tmem_addr of the thread's TMEM lane = row `row` of the tile) -> staged in
+// shared memory -> reduced into global rows by index with 16-byte vector reductions; NC/4 neighbouring lanes cover one
+// row, so a warp instruction adds whole 128-byte (NC = 32) or 256-byte (NC = 64) row slices.  `stage` holds 128 rows of
+// NC floats (16-byte chunk c of row r at position c ^ (r & 7) of its 128-byte group); a warp only touches the 32 rows of
+// its own lanes, so a warp-level sync suffices.  (A TMA bulk reduce-add per row was measured slower than this.)
+template <int NC>
 __device__ __forceinline__ void reduce_rows(uint8_t* stage, uint32_t tmem_addr, float* __restrict__ base, int64_t row_stride, int my_row,
-                                            int tid, int warp, int lane) {
-  // stage: row-major [128][NCOLS] floats, 16-byte chunk c of row r at chunk position c ^ (r & 7) within each 128-byte group
-  float* srow = reinterpret_cast<float*>(stage) + tid * NCOLS;
+                                            int row) {
+  const int lane = row & 31, qwarp = row >> 5;
+  float* srow = reinterpret_cast<float*>(stage) + row * NC;
 #pragma unroll
-  for (int c = 0; c < NCOLS / 32; ++c) {
+  for (int c = 0; c < NC / 32; ++c) {
     uint32_t r[32];
     tmem_ld32(tmem_addr + c * 32, r);
-    tmem_ld_wait();
+    tmem_ld_fence(r);
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
-      const int chunk = (c * 32 + i) >> 2;                          // 16-byte chunk index in the row
-      const int sw = (chunk & ~7) | ((chunk ^ tid) & 7);
+      const int chunk = (c * 32 + i) >> 2;
+      const int sw = (chunk & ~7) | ((chunk ^ row) & 7);
       *reinterpret_cast<uint4*>(srow + sw * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
     }
   }
   __syncwarp();
-  constexpr int CPR = NCOLS / 4;            // 16-byte chunks per row: 16 or 32
-  constexpr int RPI = 32 / CPR;             // rows per warp instruction: 2 or 1
+  constexpr int CPR = NC / 4;               // 16-byte chunks per row: 8, 16 (or 32)
+  constexpr int RPI = 32 / CPR;             // rows per warp instruction
 #pragma unroll
   for (int i = 0; i < 32 / RPI; ++i) {
     const int rl = i * RPI + lane / CPR;
     const int dst_row = __shfl_sync(0xffffffffu, my_row, rl);
-    const int row = warp * 32 + rl;
+    const int rr = qwarp * 32 + rl;
     const int chunk = lane % CPR;
-    const int sw = (chunk & ~7) | ((chunk ^ row) & 7);
-    const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + row * NCOLS + sw * 4);
+    const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
+    const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + rr * NC + sw * 4);
     if (dst_row >= 0) red_add_v4(base + (int64_t)dst_row * row_stride + chunk * 4, v.x, v.y, v.z, v.w);
   }
   __syncwarp();
 }
 
+// One work item: the key rows of a CTA and its list of query tiles.
+struct BwdItem {
+  int krow;                  // local key row fetched / owned by thread tid (-1: none)
+  int qt_first, qt_count;    // natural-order query tiles [qt_first, qt_first + qt_count) ...
+  bool q_sorted;             // ... or, when set, qt_count tiles of sorted positions starting at q_pos0 (modulo m_q)
+  int q_pos0;
+  int k_tile;
+};
+
+__device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item, int seg, int items_blk, int n_chunks, int tid) {
+  BwdItem it;
+  const bool hyper = p.mode == HA_MODE_HYPER;
+  const int n_qt = (p.m_q + TILE - 1) / TILE;
+  it.krow = -1;
+  it.qt_first = 0;
+  it.qt_count = 0;
+  it.q_sorted = false;
+  it.q_pos0 = 0;
+  if (hyper && item < items_blk) {
+    it.k_tile = item;
+    it.krow = p.k_idx[(long long)seg * p.m_k + it.k_tile * TILE + tid];
+    const int bs = (p.block_size + TILE - 1) / TILE;
+    const Window w = block_window(it.k_tile, bs, p.m_q, p.flags & HA_FLAG_SMOOTH);
+    it.q_sorted = true;
+    it.q_pos0 = w.first;
+    it.qt_count = w.count / TILE;
+  } else {
+    const int i2 = hyper ? item - items_blk : item;
+    it.k_tile = i2 / n_chunks;
+    const int z = i2 - it.k_tile * n_chunks;
+    const int kr = it.k_tile * TILE + tid;
+    if (hyper) it.krow = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + kr] : kr;
+    else it.krow = kr < p.m_k ? kr : -1;
+    it.qt_first = z * BWD_CHUNK;
+    if (!hyper && (p.flags & HA_FLAG_CAUSAL)) it.qt_first = max(it.qt_first, it.k_tile);
+    it.qt_count = min((z + 1) * BWD_CHUNK, n_qt) - it.qt_first;
+  }
+  return it;
+}
+
+// local query row of thread tid in list entry jj of an item (-1: none)
+__device__ __forceinline__ int bwd_q_row(const ha_attn_params& p, const BwdItem& it, int seg, int jj, int tid) {
+  if (jj >= it.qt_count) return -1;
+  if (it.q_sorted) {
+    int pos = it.q_pos0 + jj * TILE + tid;
+    if (pos >= p.m_q) pos -= p.m_q;
+    return p.q_idx[(long long)seg * p.m_q + pos];
+  }
+  const int r = (it.qt_first + jj) * TILE + tid;
+  return r < p.m_q ? r : -1;
+}
+
 template <typename T, int D, int DV>
-__global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const ha_attn_params p, int items_blk, int n_chunks) {
+__global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p, int items_blk, int n_chunks, int pf_dist) {
   using Cfg = BwdCfg<D, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -104,39 +172,19 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const ha_attn_params p
   __shared__ uint64_t mma_bar;
   __shared__ uint32_t tmem_slot;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // 256 threads = two groups of 128.  Thread (wg, row): TMEM lane `row`; in the elementwise phase group wg handles key
+  // columns [64 wg, 64 wg + 64) of that row, in the reductions the column half wg of its row.
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int row = tid & 127, wg = tid >> 7, qwarp = (tid >> 5) & 3;
   const bool hyper = p.mode == HA_MODE_HYPER;
   const bool causal = p.flags & HA_FLAG_CAUSAL;
   const int seg = blockIdx.y;
   const int item = blockIdx.x;
   const SegInfo si = seg_info(p, seg);
-  const int n_qt = (p.m_q + TILE - 1) / TILE;
 
   // ---- decode the work item: key rows of this CTA and its list of query tiles ----
-  int krow = -1;                 // local key row fetched / owned by this thread
-  int qt_first = 0, qt_count = 0;
-  bool q_sorted = false;         // query tiles addressed through q_idx (positions modulo m) or natural rows
-  int q_pos0 = 0;                // sorted position of the first query of the list (hyper block part)
-  int k_tile = 0;
-  if (hyper && item < items_blk) {
-    k_tile = item;
-    krow = p.k_idx[(long long)seg * p.m_k + k_tile * TILE + tid];
-    const int bs = (p.block_size + TILE - 1) / TILE;
-    const Window w = block_window(k_tile, bs, p.m_q, p.flags & HA_FLAG_SMOOTH);
-    q_sorted = true;
-    q_pos0 = w.first;
-    qt_count = w.count / TILE;
-  } else {
-    const int it = hyper ? item - items_blk : item;
-    k_tile = it / n_chunks;
-    const int z = it - k_tile * n_chunks;
-    const int kr = k_tile * TILE + tid;
-    if (hyper) krow = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + kr] : kr;
-    else krow = kr < p.m_k ? kr : -1;
-    qt_first = z * BWD_CHUNK;
-    if (!hyper && causal) qt_first = max(qt_first, k_tile);
-    qt_count = min((z + 1) * BWD_CHUNK, n_qt) - qt_first;
-  }
+  const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row);
+  const int krow = me.krow, qt_first = me.qt_first, qt_count = me.qt_count, k_tile = me.k_tile;
   if (qt_count <= 0) return;     // uniform over the CTA; nothing allocated yet
 
   const uint32_t bar = smem_u32(&mma_bar);
@@ -144,7 +192,7 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const ha_attn_params p
     mbar_init(bar, 1);
     mbar_fence_init();
   }
-  if (warp == 0) tmem_alloc(smem_u32(&tmem_slot), 512);
+  if (tid < 32) tmem_alloc(smem_u32(&tmem_slot), 512);
 
   const long long head0 = ((long long)(si.b * p.H + si.h)) * p.n;
   const uint16_t* qbase = (const uint16_t*)p.q + si.b * p.q_sb + si.h * p.q_sh + si.q_row0 * p.q_sn;
@@ -155,37 +203,52 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const ha_attn_params p
   const float* delta_base = p.delta + head0 + si.q_row0;
   float* dq_base = p.dq_acc + (head0 + si.q_row0) * D;
 
-  // local query row of thread `tid` in list entry jj (-1: none)
-  auto q_row = [&](int jj) -> int {
-    if (jj >= qt_count) return -1;
-    if (q_sorted) {
-      int pos = q_pos0 + jj * TILE + tid;
-      if (pos >= p.m_q) pos -= p.m_q;
-      return p.q_idx[(long long)seg * p.m_q + pos];
-    }
-    const int r = (qt_first + jj) * TILE + tid;
-    return r < p.m_q ? r : -1;
+  auto q_row = [&](int jj) -> int { return bwd_q_row(p, me, seg, jj, row); };
+  // group 0 fetches the K / Q tiles, group 1 the V / dO tiles
+  auto fetch_kv = [&]() {
+    if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_K, kbase, p.k_sn, krow, qwarp, lane);
+    else bwd_gather_tile<DV>(s_base + Cfg::OFF_V, vbase, p.v_sn, krow, qwarp, lane);
+  };
+  auto fetch_q = [&](int stage, int qr) {
+    if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_Q + stage * Cfg::Q_BYTES, qbase, p.q_sn, qr, qwarp, lane);
+    else bwd_gather_tile<DV>(s_base + Cfg::OFF_DO + stage * Cfg::DO_BYTES, gbase, p.do_sn, qr, qwarp, lane);
   };
 
   constexpr float LOG2E = 1.4426950408889634f;
   const float scale2 = p.scale * LOG2E;
 
   // ---- prologue: K, V tiles and query tile 0 ----
-  bwd_gather_tile<D>(s_base + Cfg::OFF_K, kbase, p.k_sn, krow, warp, lane);
-  bwd_gather_tile<DV>(s_base + Cfg::OFF_V, vbase, p.v_sn, krow, warp, lane);
+  fetch_kv();
   int qrow_cur = q_row(0);
-  bwd_gather_tile<D>(s_base + Cfg::OFF_Q, qbase, p.q_sn, qrow_cur, warp, lane);
-  bwd_gather_tile<DV>(s_base + Cfg::OFF_DO, gbase, p.do_sn, qrow_cur, warp, lane);
+  fetch_q(0, qrow_cur);
   cp_async_commit();
   float lse_cur = qrow_cur >= 0 ? lse_base[qrow_cur] * LOG2E : INFINITY;
   float delta_cur = qrow_cur >= 0 ? delta_base[qrow_cur] : 0.f;
   int qrow_next = q_row(1);
 
+  // ---- rows of the work item that runs pf_dist CTAs later: index loads now, L2 prefetches after the first pair ----
+  constexpr int PF_TILES = 4;
+  int pf_k = -1, pf_q[PF_TILES];
+#pragma unroll
+  for (int i = 0; i < PF_TILES; ++i) pf_q[i] = -1;
+  SegInfo pf_si = si;
+  {
+    const long long lin = (long long)blockIdx.y * gridDim.x + blockIdx.x + pf_dist;
+    if (hyper && pf_dist > 0 && lin < (long long)gridDim.x * gridDim.y) {
+      const int pseg = (int)(lin / gridDim.x), pitem = (int)(lin - (long long)pseg * gridDim.x);
+      pf_si = seg_info(p, pseg);
+      const BwdItem nx = bwd_decode(p, pitem, pseg, items_blk, n_chunks, row);
+      if (pitem < items_blk || p.sample_idx) pf_k = nx.krow;   // default sampled rows (0..S-1) stay hot in L2 anyway
+#pragma unroll
+      for (int i = 0; i < PF_TILES; ++i) pf_q[i] = bwd_q_row(p, nx, pseg, i, row);
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
+  const uint32_t lane_sel = (uint32_t)(qwarp * 32) << 16;
   const uint32_t tS = tmem + Cfg::COL_S, tDP = tmem + Cfg::COL_DP, tDV = tmem + Cfg::COL_DV, tDK = tmem + Cfg::COL_DK,
                  tDQ = tmem + Cfg::COL_DQ;
   constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -198,138 +261,255 @@ __global__ void __launch_bounds__(128) attn_tc_bwd_kernel(const ha_attn_params p
 
   uint32_t phase = 0;
   bool failed = false;
+  HA_T_DECL(8)
 
-  for (int jj = 0; jj < qt_count; ++jj) {
-    const int st = Cfg::STAGES == 2 ? (jj & 1) : 0;
-    const uint32_t sQ = s_base + Cfg::OFF_Q + st * Cfg::Q_BYTES;
-    const uint32_t sDO = s_base + Cfg::OFF_DO + st * Cfg::DO_BYTES;
-    float lse_next = INFINITY, delta_next = 0.f;
-    if (Cfg::STAGES == 2) {
-      if (jj + 1 < qt_count) {
-        bwd_gather_tile<D>(s_base + Cfg::OFF_Q + (st ^ 1) * Cfg::Q_BYTES, qbase, p.q_sn, qrow_next, warp, lane);
-        bwd_gather_tile<DV>(s_base + Cfg::OFF_DO + (st ^ 1) * Cfg::DO_BYTES, gbase, p.do_sn, qrow_next, warp, lane);
-        if (qrow_next >= 0) { lse_next = lse_base[qrow_next] * LOG2E; delta_next = delta_base[qrow_next]; }
-      }
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+  // S = Q K^T and dP = dO V^T of the query tile in stage `stg`
+  auto issue_mma1 = [&](int stg) {
+    const uint32_t sQ = s_base + Cfg::OFF_Q + stg * Cfg::Q_BYTES, sDO = s_base + Cfg::OFF_DO + stg * Cfg::DO_BYTES;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
+      mma_ss(tS, smem_desc(sQ + off, 16, 1024), smem_desc(s_base + Cfg::OFF_K + off, 16, 1024), id_s, kk > 0);
     }
-    const int qrow_after = q_row(jj + 2);
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    // ---- S = Q K^T and dP = dO V^T ----
-    if (tid == 0) {
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-        mma_ss(tS, smem_desc(sQ + off, 16, 1024), smem_desc(s_base + Cfg::OFF_K + off, 16, 1024), id_s, kk > 0);
-      }
-#pragma unroll
-      for (int kk = 0; kk < DV / 16; ++kk) {
-        const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-        mma_ss(tDP, smem_desc(sDO + off, 16, 1024), smem_desc(s_base + Cfg::OFF_V + off, 16, 1024), id_s, kk > 0);
-      }
-      mma_commit(bar);
+    for (int kk = 0; kk < DV / 16; ++kk) {
+      const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
+      mma_ss(tDP, smem_desc(sDO + off, 16, 1024), smem_desc(s_base + Cfg::OFF_V + off, 16, 1024), id_s, kk > 0);
     }
-    if (!mbar_wait(bar, phase)) failed = true;
-    phase ^= 1;
-    tc_fence_after();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-
-    // ---- P and dS for this thread's query row ----
-    int limit = TILE;   // visible key columns (causal diagonal pair only)
-    if (!hyper && causal && qt_first + jj == k_tile) limit = tid + 1;
+  };
+  // dV += P^T dO, dK += dS^T Q, dQ = dS K for the query tile in stage `stg`
+  auto issue_mma2 = [&](int stg, uint32_t acc0, uint32_t t_dq) {
+    const uint32_t sQ = s_base + Cfg::OFF_Q + stg * Cfg::Q_BYTES, sDO = s_base + Cfg::OFF_DO + stg * Cfg::DO_BYTES;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int kk = 0; kk < TILE / 16; ++kk)
+      mma_ss(tDV, smem_desc(s_base + Cfg::OFF_P + kk * 2048, TILE * 128, 1024), smem_desc(sDO + kk * 2048, TILE * 128, 1024), id_dv,
+             acc0 | (kk > 0));
+#pragma unroll
+    for (int kk = 0; kk < TILE / 16; ++kk)
+      mma_ss(tDK, smem_desc(s_base + Cfg::OFF_DS + kk * 2048, TILE * 128, 1024), smem_desc(sQ + kk * 2048, TILE * 128, 1024), id_dk,
+             acc0 | (kk > 0));
+#pragma unroll
+    for (int kk = 0; kk < TILE / 16; ++kk) {
+      const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
+      mma_ss(t_dq, smem_desc(s_base + Cfg::OFF_DS + off, 16, 1024), smem_desc(s_base + Cfg::OFF_K + kk * 2048, TILE * 128, 1024), id_dq,
+             kk > 0);
+    }
+  };
+  // P and dS of this thread's query row, its group's 64 key columns -> shared memory
+  auto elementwise = [&](float lse2, float dlt, bool masked) {
+    const int limit = masked ? row + 1 : TILE;
+    const uint64_t sc2 = pack_f2(scale2, scale2), nlse = pack_f2(-lse2, -lse2);
+    const uint64_t scl = pack_f2(p.scale, p.scale), ndel = pack_f2(-dlt * p.scale, -dlt * p.scale);
+    const int col0 = wg * 64;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
       uint32_t rs[32], rp[32];
-      tmem_ld32(tS + lane_sel + c * 32, rs);
-      tmem_ld32(tDP + lane_sel + c * 32, rp);
-      tmem_ld_wait();
+      tmem_ld32(tS + lane_sel + col0 + c * 32, rs);
+      tmem_ld32(tDP + lane_sel + col0 + c * 32, rp);
+      tmem_ld_fence(rs);
+      tmem_ld_fence(rp);
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
         uint32_t pw[4], dw[4];
 #pragma unroll
         for (int e = 0; e < 8; e += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(rs[i + e]), scale2, -lse_cur));
-          float p1 = fast_exp2(fmaf(__uint_as_float(rs[i + e + 1]), scale2, -lse_cur));
-          if (c * 32 + i + e >= limit) p0 = 0.f;
-          if (c * 32 + i + e + 1 >= limit) p1 = 0.f;
-          const float d0 = p0 * (__uint_as_float(rp[i + e]) - delta_cur) * p.scale;
-          const float d1 = p1 * (__uint_as_float(rp[i + e + 1]) - delta_cur) * p.scale;
+          float p0, p1, d0, d1;
+          unpack_f2(ffma2(pack_u2(rs[i + e], rs[i + e + 1]), sc2, nlse), p0, p1);
+          p0 = fast_exp2(p0);
+          p1 = fast_exp2(p1);
+          if (masked) {
+            if (col0 + c * 32 + i + e >= limit) p0 = 0.f;
+            if (col0 + c * 32 + i + e + 1 >= limit) p1 = 0.f;
+          }
+          // ds = p * (dp - delta) * scale
+          unpack_f2(fmul2(pack_f2(p0, p1), ffma2(pack_u2(rp[i + e], rp[i + e + 1]), scl, ndel)), d0, d1);
           pw[e >> 1] = pack2<T>(p0, p1);
           dw[e >> 1] = pack2<T>(d0, d1);
         }
-        const uint32_t off = swz_off(TILE, tid, c * 32 + i);
+        const uint32_t off = swz_off(TILE, row, col0 + c * 32 + i);
         *reinterpret_cast<uint4*>(sP + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
         *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
       }
     }
+  };
+  auto prefetch_next_item = [&]() {
+    if (wg != 0) return;
+    const uint16_t* pq = (const uint16_t*)p.q + pf_si.b * p.q_sb + pf_si.h * p.q_sh + pf_si.q_row0 * p.q_sn;
+    const uint16_t* pg = (const uint16_t*)p.d_o + pf_si.b * p.do_sb + pf_si.h * p.do_sh + pf_si.q_row0 * p.do_sn;
+    if (pf_k >= 0) {
+      const uint16_t* pk = (const uint16_t*)p.k + pf_si.b * p.k_sb + pf_si.h * p.k_sh + (pf_si.k_row0 + pf_k) * p.k_sn;
+      const uint16_t* pv = (const uint16_t*)p.v + pf_si.b * p.v_sb + pf_si.h * p.v_sh + (pf_si.k_row0 + pf_k) * p.v_sn;
+      prefetch_l2(pk);
+      if (D > 64) prefetch_l2(pk + 64);
+      prefetch_l2(pv);
+      if (DV > 64) prefetch_l2(pv + 64);
+    }
+#pragma unroll
+    for (int i = 0; i < PF_TILES; ++i) {
+      if (pf_q[i] >= 0) {
+        prefetch_l2(pq + (int64_t)pf_q[i] * p.q_sn);
+        if (D > 64) prefetch_l2(pq + (int64_t)pf_q[i] * p.q_sn + 64);
+        prefetch_l2(pg + (int64_t)pf_q[i] * p.do_sn);
+        if (DV > 64) prefetch_l2(pg + (int64_t)pf_q[i] * p.do_sn + 64);
+      }
+    }
+  };
+  const bool diag_possible = !hyper && causal;
+
+  if constexpr (Cfg::PIPE) {
+    // ------------------------------------------------------------------------------------------------------------
+    // Pipelined schedule.  batch(j) = { dV, dK, dQ of pair j ; S, dP of pair j+1 } is one commit.  While it runs, the
+    // threads reduce dQ of pair j-1 (its own TMEM buffer, its own staging tile); the next pair's elementwise phase
+    // starts as soon as the batch has landed.
+    // ------------------------------------------------------------------------------------------------------------
+    uint8_t* sSTG = smem + Cfg::OFF_STG;
+    if (qt_count > 1) {                       // query tile 1 goes into stage 1 right away
+      fetch_q(1, qrow_next);
+    }
+    cp_async_commit();
+    float lse_next = INFINITY, delta_next = 0.f;
+    if (qt_count > 1 && qrow_next >= 0) { lse_next = lse_base[qrow_next] * LOG2E; delta_next = delta_base[qrow_next]; }
+    cp_async_wait<1>();                       // K, V, query tile 0
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-
-    // ---- dV += P^T dO, dK += dS^T Q, dQ = dS K ----
     if (tid == 0) {
-      const uint32_t acc0 = jj > 0;
-#pragma unroll
-      for (int kk = 0; kk < TILE / 16; ++kk) {
-        mma_ss(tDV, smem_desc(s_base + Cfg::OFF_P + kk * 2048, TILE * 128, 1024), smem_desc(sDO + kk * 2048, TILE * 128, 1024), id_dv,
-               acc0 | (kk > 0));
-      }
-#pragma unroll
-      for (int kk = 0; kk < TILE / 16; ++kk) {
-        mma_ss(tDK, smem_desc(s_base + Cfg::OFF_DS + kk * 2048, TILE * 128, 1024), smem_desc(sQ + kk * 2048, TILE * 128, 1024), id_dk,
-               acc0 | (kk > 0));
-      }
-#pragma unroll
-      for (int kk = 0; kk < TILE / 16; ++kk) {
-        const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-        mma_ss(tDQ, smem_desc(s_base + Cfg::OFF_DS + off, 16, 1024), smem_desc(s_base + Cfg::OFF_K + kk * 2048, TILE * 128, 1024), id_dq,
-               kk > 0);
-      }
+      issue_mma1(0);
       mma_commit(bar);
     }
-    if (!mbar_wait(bar, phase)) failed = true;
-    phase ^= 1;
-    tc_fence_after();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-
-    // ---- dQ rows: TMEM -> staging (the P tile is idle now) -> fp32 reductions ----
-    reduce_rows<D>(sP, tDQ + lane_sel, dq_base, D, qrow_cur, tid, warp, lane);
-    if (Cfg::STAGES == 1 && jj + 1 < qt_count) {
-      // single-stage variant: fetch the next query tile now that every MMA reading this one has completed
-      __syncthreads();
-      bwd_gather_tile<D>(s_base + Cfg::OFF_Q, qbase, p.q_sn, qrow_next, warp, lane);
-      bwd_gather_tile<DV>(s_base + Cfg::OFF_DO, gbase, p.do_sn, qrow_next, warp, lane);
+    int qrow_prev = -1;
+    for (int jj = 0; jj < qt_count; ++jj) {
+      HA_T_MARK(0)
+      const int st = jj & 1;
+      if (!mbar_wait(bar, phase)) failed = true;     // batch(jj-1): S, dP of this pair are in TMEM
+      phase ^= 1;
+      tc_fence_after();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      HA_T_MARK(1)
+      // stage st^1 is free now (its last reader was batch(jj-1)): fetch query tile jj+1 (tile 1 is already there)
+      int qrow_after = -1;
+      float lse_after = INFINITY, delta_after = 0.f;
+      if (jj >= 1 && jj + 1 < qt_count) fetch_q(st ^ 1, qrow_next);
       cp_async_commit();
-      if (qrow_next >= 0) { lse_next = lse_base[qrow_next] * LOG2E; delta_next = delta_base[qrow_next]; }
+      if (jj + 2 < qt_count) {
+        qrow_after = q_row(jj + 2);
+      }
+      HA_T_MARK(2)
+      elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile);
+      HA_T_MARK(3)
+      cp_async_wait<0>();                     // query tile jj+1 has landed
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      tc_fence_after();
+      if (tid == 0) {
+        issue_mma2(st, jj > 0, tDQ + (jj & 1) * D);
+        if (jj + 1 < qt_count) issue_mma1(st ^ 1);
+        mma_commit(bar);
+      }
+      HA_T_MARK(4)
+      // underneath the batch: dQ of the previous pair
+      if (jj >= 1)
+        reduce_rows<D / 2>(sSTG + wg * Cfg::STG_HALF, tDQ + ((jj - 1) & 1) * D + lane_sel + wg * (D / 2), dq_base + wg * (D / 2), D,
+                           qrow_prev, row);
+      HA_T_MARK(5)
+      if (jj == 0) prefetch_next_item();
+      // rotate the per-tile registers; lse/delta of tile jj+2 are loaded here so that they arrive during the next pair
+      qrow_prev = qrow_cur;
+      qrow_cur = qrow_next;
+      lse_cur = lse_next;
+      delta_cur = delta_next;
+      qrow_next = qrow_after;
+      if (qrow_after >= 0) { lse_after = lse_base[qrow_after] * LOG2E; delta_after = delta_base[qrow_after]; }
+      lse_next = lse_after;
+      delta_next = delta_after;
     }
-    qrow_cur = qrow_next;
-    qrow_next = qrow_after;
-    lse_cur = lse_next;
-    delta_cur = delta_next;
+    cp_async_wait<0>();
+    if (!failed) {
+      if (!mbar_wait(bar, phase)) failed = true;     // last batch
+      phase ^= 1;
+      tc_fence_after();
+      failed = __syncthreads_or(failed);
+    }
+    HA_T_MARK(6)
+    if (!failed)
+      reduce_rows<D / 2>(sSTG + wg * Cfg::STG_HALF, tDQ + ((qt_count - 1) & 1) * D + lane_sel + wg * (D / 2), dq_base + wg * (D / 2), D,
+                         qrow_prev, row);
+  } else {
+    // ------------------------------------------------------------------------------------------------------------
+    // Serial schedule (head dim 128: TMEM has no room for a separate dQ buffer, shared memory none for a second stage)
+    // ------------------------------------------------------------------------------------------------------------
+    for (int jj = 0; jj < qt_count; ++jj) {
+      HA_T_MARK(0)
+      cp_async_wait<0>();
+      const int qrow_after = q_row(jj + 2);
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      tc_fence_after();
+      HA_T_MARK(1)
+      if (tid == 0) {
+        issue_mma1(0);
+        mma_commit(bar);
+      }
+      if (!mbar_wait(bar, phase)) failed = true;
+      phase ^= 1;
+      tc_fence_after();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      HA_T_MARK(2)
+      elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile);
+      fence_async_smem();
+      tc_fence_before();
+      __syncthreads();
+      tc_fence_after();
+      HA_T_MARK(3)
+      if (tid == 0) {
+        issue_mma2(0, jj > 0, tDQ);
+        mma_commit(bar);
+      }
+      if (!mbar_wait(bar, phase)) failed = true;
+      phase ^= 1;
+      tc_fence_after();
+      if (__syncthreads_or(failed)) { failed = true; break; }
+      HA_T_MARK(4)
+      // dQ rows: TMEM -> staging (the P / dS tiles are idle now) -> fp32 reductions; each group one column half
+      reduce_rows<D / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDQ + lane_sel + wg * (D / 2), dq_base + wg * (D / 2), D, qrow_cur, row);
+      HA_T_MARK(5)
+      float lse_next = INFINITY, delta_next = 0.f;
+      if (jj + 1 < qt_count) {
+        // fetch the next query tile now that every MMA reading this one has completed
+        __syncthreads();
+        fetch_q(0, qrow_next);
+        cp_async_commit();
+        if (qrow_next >= 0) { lse_next = lse_base[qrow_next] * LOG2E; delta_next = delta_base[qrow_next]; }
+      }
+      qrow_cur = qrow_next;
+      qrow_next = qrow_after;
+      lse_cur = lse_next;
+      delta_cur = delta_next;
+      if (jj == 0) prefetch_next_item();
+    }
+    cp_async_wait<0>();
+    HA_T_MARK(6)
   }
-  cp_async_wait<0>();
 
   if (failed) {
     if (tid == 0 && p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
   } else {
-    // dK / dV rows of this key tile (lanes = keys) -> reductions into the accumulators
+    // dK / dV rows of this key tile (lanes = keys) -> reductions into the accumulators, one column half per group;
+    // the staging rows are private per warp, so consecutive reductions can share them
     __syncthreads();
     float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
     float* dv_base = p.dv_acc + (head0 + si.k_row0) * DV;
-    // the staging area (P and dS tiles, contiguous) is private per warp, so the two reductions can share it
-    reduce_rows<DV>(sP, tDV + lane_sel, dv_base, DV, krow, tid, warp, lane);
-    reduce_rows<D>(sP, tDK + lane_sel, dk_base, D, krow, tid, warp, lane);
+    reduce_rows<DV / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, krow, row);
+    reduce_rows<D / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, krow, row);
   }
+  HA_T_MARK(7)
+  HA_T_DUMP(8, (int)(blockIdx.y * gridDim.x + blockIdx.x), tid == 0)
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 512);
+  if (tid < 32) tmem_dealloc(tmem, 512);
 }
 
 template <typename T, int D, int DV>
@@ -350,7 +530,11 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   if (items > 0x7fffffffLL || segs > 65535) return HA_ERR_INVALID;
   HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_bwd_kernel<T, D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
              "ha_attn_bwd smem attribute");
-  attn_tc_bwd_kernel<T, D, DV><<<dim3((unsigned)items, (unsigned)segs), 128, Cfg::SMEM, st>>>(p, items_blk, n_chunks);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int pf_dist = p.mode == HA_MODE_HYPER ? sms : 0;   // one CTA per SM is resident: the next wave is `sms` items away
+  attn_tc_bwd_kernel<T, D, DV><<<dim3((unsigned)items, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist);
   HA_LAUNCHED("ha_attn_bwd (tcgen05)");
   return HA_OK;
 }
@@ -386,3 +570,5 @@ int tc_attn_bwd(const ha_attn_params& p, cudaStream_t st) {
 }
 
 }  // namespace ha
+
+HA_T_SETTER(ha_debug_set_timing_buffer_bwd)

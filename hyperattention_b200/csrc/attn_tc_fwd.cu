@@ -15,7 +15,8 @@
 //     in-place combine), round, stage through shared memory and store whole rows coalesced.
 // The same kernel serves both patterns; only the list of key tiles of a query tile differs:
 //   hyper: block-window tiles through k_idx, then the sampled rows;   flash: contiguous tiles, causal mask.
-// TMEM budget per CTA: 128 (S) + 64 (P, packed pairs) + DV (PV) columns -> 256 for DV = 64, two CTAs per SM.
+// TMEM budget per CTA: two regions of 128 columns (S; P in place; PV in the freed half) -> 256 for DV = 64, two CTAs
+// per SM; the MMAs of one key tile and the S MMA of the next are issued as one batch (one commit per key tile).
 #include "attn_index.cuh"
 
 #include <type_traits>
@@ -32,8 +33,12 @@ template <int D, int DV> struct FwdCfg {
   static constexpr int OFF_V = OFF_K + 2 * K_BYTES;        // two stages
   static constexpr int OFF_OLD = OFF_V + 2 * V_BYTES;      // previous o rows (merge) / output staging
   static constexpr int SMEM = OFF_OLD + O_BYTES + 1024;    // + alignment slack
-  static constexpr int TMEM_COLS = (128 + 64 + DV) <= 256 ? 256 : 512;
-  static constexpr int COL_S = 0, COL_P = 128, COL_PV = 192;
+  // TMEM: two regions (key tiles alternate).  A region holds S (128 fp32 columns); P is written in place over its first
+  // 64 columns as S is consumed; the P.V product lands in the columns S no longer needs (DV = 64: the upper half of the
+  // same 128 columns; DV = 128: 128 further columns).
+  static constexpr int REGION = DV <= 64 ? 128 : 256;
+  static constexpr int PV_OFF = DV <= 64 ? 64 : 128;
+  static constexpr int TMEM_COLS = 2 * REGION;
 };
 
 // 128 rows x COLS elements (2 bytes each) gathered by row index into swizzled slabs; 8 lanes per row.
@@ -81,7 +86,7 @@ struct TileList {
 };
 
 template <typename T, int D, int DV>
-__global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p) {
+__global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p, const int pf_dist) {
   using Cfg = FwdCfg<D, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -153,125 +158,243 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   cp_async_commit();
   int krow_next = key_row(1);
 
+  // ---- rows of the query tile that runs pf_dist CTAs later (one wave ahead): pulled into L2 while this CTA computes,
+  //      so that tile's dependent index -> row gathers hit L2 instead of HBM.  Index loads are issued here, the prefetches
+  //      after the first key tile, when the indices have arrived.
+  constexpr int PF_TILES = 4;
+  int pf_q = -1, pf_k[PF_TILES];
+#pragma unroll
+  for (int i = 0; i < PF_TILES; ++i) pf_k[i] = -1;
+  SegInfo pf_si = si;
+  {
+    const long long lin = (long long)blockIdx.y * gridDim.x + blockIdx.x + pf_dist;
+    if (hyper && pf_dist > 0 && lin < (long long)gridDim.x * gridDim.y) {
+      const int pseg = (int)(lin / gridDim.x), pqt = (int)(lin - (long long)pseg * gridDim.x);
+      pf_si = seg_info(p, pseg);
+      const int bs = (p.block_size + TILE - 1) / TILE;
+      const Window pw = block_window(pqt, bs, p.m_k, p.flags & HA_FLAG_SMOOTH);
+      const int pn_blk = pw.count / TILE;
+      pf_q = p.q_idx[(long long)pseg * p.m_q + pqt * TILE + tid];
+#pragma unroll
+      for (int i = 0; i < PF_TILES; ++i) {
+        if (i < pn_blk) {
+          int pos = pw.first + i * TILE + tid;
+          if (pos >= p.m_k) pos -= p.m_k;
+          pf_k[i] = p.k_idx[(long long)pseg * p.m_k + pos];
+        } else if (p.sample_idx && (i - pn_blk) * TILE < p.sample_size) {
+          pf_k[i] = p.sample_idx[(long long)pseg * p.sample_size + (i - pn_blk) * TILE + tid];
+        }
+      }
+    }
+  }
+
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
   const uint32_t lane_sel = (uint32_t)(warp * 32) << 16;
-  const uint32_t tS = tmem + Cfg::COL_S, tP = tmem + Cfg::COL_P, tPV = tmem + Cfg::COL_PV;
   constexpr int AB_FMT = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   const uint32_t idesc_s = mma_idesc(TILE, TILE, AB_FMT, 0, 0);
   const uint32_t idesc_pv = mma_idesc(TILE, DV, AB_FMT, 0, 1);
 
-  float o_acc[DV];
+  __align__(8) float o_acc[DV];
 #pragma unroll
   for (int i = 0; i < DV; ++i) o_acc[i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
   const float scale2 = p.scale * 1.4426950408889634f;
   uint32_t phase = 0;
   bool failed = false;
+  HA_T_DECL(8)
 
+  auto issue_s = [&](int stg, uint32_t t_s) {
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint32_t a_addr = s_base + Cfg::OFF_Q + (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
+      const uint32_t b_addr = s_base + Cfg::OFF_K + stg * Cfg::K_BYTES + (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
+      mma_ss(t_s, smem_desc(a_addr, 16, 1024), smem_desc(b_addr, 16, 1024), idesc_s, kk > 0);
+    }
+  };
+  auto issue_pv = [&](int stg, uint32_t t_p, uint32_t t_pv) {
+#pragma unroll
+    for (int kk = 0; kk < TILE / 16; ++kk) {
+      const uint32_t b_addr = s_base + Cfg::OFF_V + stg * Cfg::V_BYTES + kk * 2048;
+      mma_ts(t_pv, t_p + kk * 8, smem_desc(b_addr, TILE * 128, 1024), idesc_pv, kk > 0);
+    }
+  };
+  auto accumulate_pv = [&](uint32_t t_pv, float alpha) {
+    const uint64_t al2 = pack_f2(alpha, alpha);
+    uint64_t* o2 = reinterpret_cast<uint64_t*>(o_acc);
+#pragma unroll
+    for (int c = 0; c < DV / 32; ++c) {
+      uint32_t r[32];
+      tmem_ld32(t_pv + lane_sel + c * 32, r);
+      tmem_ld_fence(r);
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) o2[(c * 32 + i) >> 1] = ffma2(o2[(c * 32 + i) >> 1], al2, pack_u2(r[i], r[i + 1]));
+    }
+  };
+
+  // Schedule: batch(j) = { P.V of key tile j ; S of key tile j+1 } is one commit; while it runs, the other CTA on the SM
+  // has the pipes.  The product of tile j-1 is folded into the output registers at the top of iteration j.
+  cp_async_wait<0>();
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (tid == 0) {
+    issue_s(0, tmem);
+    mma_commit(bar);
+  }
+  float alpha_prev = 0.f;
   for (int j = 0; j < tl.n_tiles; ++j) {
+    HA_T_MARK(0)
     const int st = j & 1;
-    // prefetch tile j+1 into the other stage (its previous user, tile j-1, has completed both MMAs)
+    const uint32_t tS = tmem + st * Cfg::REGION, tP = tS, tPV = tS + Cfg::PV_OFF;
+    if (!mbar_wait(bar, phase)) { failed = true; }     // batch(j-1): S of this tile (and P.V of the previous one) landed
+    phase ^= 1;
+    tc_fence_after();
+    if (__syncthreads_or(failed)) { failed = true; break; }
+    HA_T_MARK(1)
+    // the other stage is free now: fetch key tile j+1
     if (j + 1 < tl.n_tiles) {
       gather_tile<D>(s_base + Cfg::OFF_K + (st ^ 1) * Cfg::K_BYTES, kbase, p.k_sn, krow_next, warp, lane);
       gather_tile<DV>(s_base + Cfg::OFF_V + (st ^ 1) * Cfg::V_BYTES, vbase, p.v_sn, krow_next, warp, lane);
     }
     cp_async_commit();
     const int krow_after = key_row(j + 2);   // index load for the tile after next, consumed next iteration
-    cp_async_wait<1>();                       // tile j (and Q) have landed
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    if (tid == 0) {
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t a_addr = s_base + Cfg::OFF_Q + (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-        const uint32_t b_addr = s_base + Cfg::OFF_K + st * Cfg::K_BYTES + (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-        mma_ss(tS, smem_desc(a_addr, 16, 1024), smem_desc(b_addr, 16, 1024), idesc_s, kk > 0);
-      }
-      mma_commit(bar);
-    }
-    if (!mbar_wait(bar, phase)) { failed = true; }
-    phase ^= 1;
-    tc_fence_after();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-
+    if (j >= 1) accumulate_pv(tmem + (st ^ 1) * Cfg::REGION + Cfg::PV_OFF, alpha_prev);
+    HA_T_MARK(2)
     // ---- softmax over this tile's 128 columns ----
-    // number of visible columns for this row: all, or clipped by the causal diagonal / end of keys
+    // visible columns of this row: all of them, except on a causal diagonal tile or a ragged last tile
     int limit = TILE;
+    bool masked = false;   // uniform over the CTA
     if (!hyper) {
       limit = min(TILE, p.m_k - j * TILE);
-      if (causal) limit = min(limit, qpos - j * TILE + 1);
-    }
-    float mx = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tS + lane_sel + c * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float s = __uint_as_float(r[i]);
-        if (c * 32 + i < limit) mx = fmaxf(mx, s);
+      masked = limit < TILE;
+      if (causal) {
+        limit = min(limit, qpos - j * TILE + 1);
+        masked = masked || (j == qt);
       }
+    }
+    float mx;
+    {
+      float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+      uint32_t ra[32], rb[32];
+      tmem_ld32(tS + lane_sel, ra);
+      tmem_ld_fence(ra);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        if (c + 1 < 4) tmem_ld32(tS + lane_sel + (c + 1) * 32, nxt);
+        if (!masked) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            m0 = fmax3(m0, __uint_as_float(cur[i]), __uint_as_float(cur[i + 1]));
+            m1 = fmax3(m1, __uint_as_float(cur[i + 2]), __uint_as_float(cur[i + 3]));
+            m2 = fmax3(m2, __uint_as_float(cur[i + 4]), __uint_as_float(cur[i + 5]));
+            m3 = fmax3(m3, __uint_as_float(cur[i + 6]), __uint_as_float(cur[i + 7]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < limit) m0 = fmaxf(m0, __uint_as_float(cur[i]));
+        }
+        if (c + 1 < 4) tmem_ld_fence(nxt);
+      }
+      mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
     }
     const float m_new = fmaxf(m_run, mx * scale2);
     const float m_use = m_new == -INFINITY ? 0.f : m_new;
     const float alpha = fast_exp2(m_run - m_use);   // m_run = -inf -> 0
-    float psum = 0.f;
+    float psum;
+    {
+      const uint64_t sc2 = pack_f2(scale2, scale2), negm = pack_f2(-m_use, -m_use);
+      uint64_t ps_a = pack_f2(0.f, 0.f), ps_b = ps_a;
+      uint32_t ra[32], rb[32];
+      tmem_ld32(tS + lane_sel, ra);
+      tmem_ld_fence(ra);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tS + lane_sel + c * 32, r);
-      tmem_ld_wait();
-      uint32_t pk[16];
+      for (int c = 0; c < 4; ++c) {
+        uint32_t(&cur)[32] = (c & 1) ? rb : ra;
+        uint32_t(&nxt)[32] = (c & 1) ? ra : rb;
+        // P chunk c below overwrites columns [16c, 16c+16), part of S chunk c/2, which is already in registers; the
+        // chunk being loaded (c+1) lies in columns >= 32(c+1), disjoint from them
+        if (c + 1 < 4) tmem_ld32(tS + lane_sel + (c + 1) * 32, nxt);
+        uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), scale2, -m_use));
-        float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), scale2, -m_use));
-        if (c * 32 + i >= limit) p0 = 0.f;
-        if (c * 32 + i + 1 >= limit) p1 = 0.f;
-        psum += p0 + p1;
-        pk[i >> 1] = pack2<T>(p0, p1);
+        for (int i = 0; i < 32; i += 4) {
+          float p0, p1, p2, p3;
+          unpack_f2(ffma2(pack_u2(cur[i], cur[i + 1]), sc2, negm), p0, p1);
+          unpack_f2(ffma2(pack_u2(cur[i + 2], cur[i + 3]), sc2, negm), p2, p3);
+          p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
+          if (masked) {
+            if (c * 32 + i >= limit) p0 = 0.f;
+            if (c * 32 + i + 1 >= limit) p1 = 0.f;
+            if (c * 32 + i + 2 >= limit) p2 = 0.f;
+            if (c * 32 + i + 3 >= limit) p3 = 0.f;
+          }
+          ps_a = fadd2(ps_a, pack_f2(p0, p1));
+          ps_b = fadd2(ps_b, pack_f2(p2, p3));
+          pk[i >> 1] = pack2<T>(p0, p1);
+          pk[(i >> 1) + 1] = pack2<T>(p2, p3);
+        }
+        tmem_st16(tP + lane_sel + c * 16, pk);
+        if (c + 1 < 4) tmem_ld_fence(nxt);
       }
-      tmem_st16(tP + lane_sel + c * 16, pk);
+      float s0, s1;
+      unpack_f2(fadd2(ps_a, ps_b), s0, s1);
+      psum = s0 + s1;
     }
     tmem_st_wait();
     l_run = l_run * alpha + psum;
     m_run = m_new;
+    alpha_prev = alpha;
+    HA_T_MARK(3)
+    cp_async_wait<0>();                        // key tile j+1 has landed
+    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-
     if (tid == 0) {
-#pragma unroll
-      for (int kk = 0; kk < TILE / 16; ++kk) {
-        const uint32_t b_addr = s_base + Cfg::OFF_V + st * Cfg::V_BYTES + kk * 2048;
-        mma_ts(tPV, tP + kk * 8, smem_desc(b_addr, TILE * 128, 1024), idesc_pv, kk > 0);
-      }
+      issue_pv(st, tP, tPV);
+      if (j + 1 < tl.n_tiles) issue_s(st ^ 1, tmem + (st ^ 1) * Cfg::REGION);
       mma_commit(bar);
     }
-    if (!mbar_wait(bar, phase)) { failed = true; }
-    phase ^= 1;
-    tc_fence_after();
-    if (__syncthreads_or(failed)) { failed = true; break; }
-
-#pragma unroll
-    for (int c = 0; c < DV / 32; ++c) {
-      uint32_t r[32];
-      tmem_ld32(tPV + lane_sel + c * 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = fmaf(o_acc[c * 32 + i], alpha, __uint_as_float(r[i]));
-    }
+    HA_T_MARK(4)
     krow_cur = krow_next;
     krow_next = krow_after;
+    if (j == 0 && pf_q >= 0) {
+      const uint16_t* pq = (const uint16_t*)p.q + pf_si.b * p.q_sb + pf_si.h * p.q_sh + (pf_si.q_row0 + pf_q) * p.q_sn;
+      const uint16_t* pk = (const uint16_t*)p.k + pf_si.b * p.k_sb + pf_si.h * p.k_sh + pf_si.k_row0 * p.k_sn;
+      const uint16_t* pv = (const uint16_t*)p.v + pf_si.b * p.v_sb + pf_si.h * p.v_sh + pf_si.k_row0 * p.v_sn;
+      prefetch_l2(pq);
+      if (D > 64) prefetch_l2(pq + 64);
+      if (merge) {
+        const uint16_t* po = (const uint16_t*)p.o + pf_si.b * p.o_sb + pf_si.h * p.o_sh + (pf_si.q_row0 + pf_q) * p.o_sn;
+        prefetch_l2(po);
+        if (DV > 64) prefetch_l2(po + 64);
+      }
+#pragma unroll
+      for (int i = 0; i < PF_TILES; ++i) {
+        if (pf_k[i] >= 0) {
+          prefetch_l2(pk + (int64_t)pf_k[i] * p.k_sn);
+          if (D > 64) prefetch_l2(pk + (int64_t)pf_k[i] * p.k_sn + 64);
+          prefetch_l2(pv + (int64_t)pf_k[i] * p.v_sn);
+          if (DV > 64) prefetch_l2(pv + (int64_t)pf_k[i] * p.v_sn + 64);
+        }
+      }
+    }
+    HA_T_MARK(5)
   }
   cp_async_wait<0>();
+  if (!failed) {
+    if (!mbar_wait(bar, phase)) failed = true;          // the last P.V
+    phase ^= 1;
+    tc_fence_after();
+    failed = __syncthreads_or(failed);
+    if (!failed) accumulate_pv(tmem + ((tl.n_tiles - 1) & 1) * Cfg::REGION + Cfg::PV_OFF, alpha_prev);
+  }
 
   if (failed) {
     if (tid == 0 && p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
@@ -325,6 +448,8 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
     if (qrow >= 0) p.lse[lse_at] = lse;
   }
 
+  HA_T_MARK(6)
+  HA_T_DUMP(8, (int)(blockIdx.y * gridDim.x + blockIdx.x), tid == 0)
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, Cfg::TMEM_COLS);
@@ -340,7 +465,12 @@ static int launch_fwd(const ha_attn_params& p, cudaStream_t st) {
   // per device, so set on every launch (one process may drive several GPUs)
   HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_fwd_kernel<T, D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
              "ha_attn_fwd smem attribute");
-  attn_tc_fwd_kernel<T, D, DV><<<dim3(n_qt, (unsigned)segs), 128, Cfg::SMEM, st>>>(p);
+  // CTAs resident at once (shared memory and TMEM allow two per SM at head dim 64, one otherwise) = prefetch distance
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int pf_dist = p.mode == HA_MODE_HYPER ? sms * (Cfg::TMEM_COLS == 256 ? 2 : 1) : 0;
+  attn_tc_fwd_kernel<T, D, DV><<<dim3(n_qt, (unsigned)segs), 128, Cfg::SMEM, st>>>(p, pf_dist);
   HA_LAUNCHED("ha_attn_fwd (tcgen05)");
   return HA_OK;
 }
@@ -380,3 +510,5 @@ int tc_attn_fwd(const ha_attn_params& p, cudaStream_t st) {
 }
 
 }  // namespace ha
+
+HA_T_SETTER(ha_debug_set_timing_buffer_fwd)

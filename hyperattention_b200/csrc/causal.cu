@@ -43,6 +43,47 @@ static int make_plan(const ha_causal_params& p, CausalPlan& pl) {
   return HA_OK;
 }
 
+
+// delta of every part in one pass: dO is read once per row; the leaf part is needed by every row, the rectangle of
+// depth l only by rows in the second half of their span.  Output delta[part][B*H*n], part = depth, leaves last.
+template <typename T, int EPC>
+__global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ d_o, const uint8_t* __restrict__ parts0, long long part_stride_bytes,
+                                                          int levels, int n, int lpr, float* __restrict__ delta, long long total_rows) {
+  const int lane = threadIdx.x & 31;
+  const int rpw = 32 / lpr, chunk = lane % lpr, sub = lane / lpr;
+  const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int dv = lpr * EPC;
+  for (long long base = warp_id * rpw; base < total_rows; base += n_warps * rpw) {
+    const long long row = base + sub;
+    const bool ok = row < total_rows;
+    const int i = ok ? (int)(row % n) : 0;
+    uint4 g = make_uint4(0, 0, 0, 0);
+    if (ok) g = __ldg(reinterpret_cast<const uint4*>(d_o + row * dv + chunk * EPC));
+    for (int part = 0; part <= levels; ++part) {
+      const bool need = ok && (part == levels || ((i / (n >> (part + 1))) & 1));
+      float s = 0.f;
+      if (need) {
+        const T* po = reinterpret_cast<const T*>(parts0 + part * part_stride_bytes) + row * dv + chunk * EPC;
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(po));
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          if constexpr (EPC == 8) {
+            const float2 fa = unpack2<T>(aw[w]), fg = unpack2<T>(gw[w]);
+            s = fmaf(fa.x, fg.x, s);
+            s = fmaf(fa.y, fg.y, s);
+          } else {
+            s = fmaf(__uint_as_float(aw[w]), __uint_as_float(gw[w]), s);
+          }
+        }
+      }
+      for (int off = lpr >> 1; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+      if (need && chunk == 0) delta[(long long)part * total_rows + row] = s;
+    }
+  }
+}
+
 static inline long long align256(long long x) { return (x + 255) / 256 * 256; }
 
 struct SavedLayout {
@@ -92,7 +133,7 @@ int64_t ha_causal_scratch_bytes(const ha_causal_params* p, int32_t backward) {
   CausalPlan pl;
   if (!p || make_plan(*p, pl) != HA_OK) return -1;
   if (!backward) return 2 * align256(pl.rows * 4) + align256(pl.sort_ws);
-  return align256(pl.rows * p->d * 4) * 2 + align256(pl.rows * p->dv * 4) + align256(pl.rows * 4);
+  return align256(pl.rows * p->d * 4) * 2 + align256(pl.rows * p->dv * 4) + align256(pl.rows * 4 * (p->levels + 1));
 }
 
 int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
@@ -167,10 +208,31 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
   ha_attn_params a;
   fill_attn(p, a);
   a.delta = delta; a.dq_acc = dq_acc; a.dk_acc = dk_acc; a.dv_acc = dv_acc;
+  // reference gradient convention: every part uses sum(o_part * dO) of its own output (its d(lse) is dropped);
+  // exact convention: sum(o * dO) of the merged output, computed once
+  bool fused_parts = false;
+  if (p.keep_parts) {
+    const int es = dtype_size(p.dtype), epc = 16 / es, lpr = p.dv / epc;
+    if (p.dv % epc == 0 && (lpr == 2 || lpr == 4 || lpr == 8 || lpr == 16 || lpr == 32) && (uintptr_t)p.d_o % 16 == 0) {
+      const long long part_stride = (uint8_t*)sv.part_o(1) - (uint8_t*)sv.part_o(0);
+      const long long per_cta = 8LL * (32 / lpr);
+      long long want = (pl.rows + per_cta - 1) / per_cta;
+      const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
+      if (p.dtype == HA_BF16)
+        delta_parts_kernel<__nv_bfloat16, 8><<<grid, 256, 0, st>>>((const __nv_bfloat16*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows);
+      else if (p.dtype == HA_FP16)
+        delta_parts_kernel<__half, 8><<<grid, 256, 0, st>>>((const __half*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows);
+      else
+        delta_parts_kernel<float, 4><<<grid, 256, 0, st>>>((const float*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows);
+      HA_LAUNCHED("ha_causal_bwd delta");
+      fused_parts = true;
+    }
+  }
   auto part_delta = [&](int part) -> int {
-    // reference gradient convention: every part uses sum(o_part * dO) of its own output (its d(lse) is dropped);
-    // exact convention: sum(o * dO) of the merged output, computed once
+    if (fused_parts) { a.delta = delta + (long long)part * pl.rows; return HA_OK; }
+    if (!p.keep_parts && part != p.levels) return HA_OK;   // one delta from the merged output serves every part
     const void* o_src = p.keep_parts ? sv.part_o(part) : p.o;
+    a.delta = delta;
     return ha_delta(o_src, a.o_sb, a.o_sh, a.o_sn, p.d_o, a.do_sb, a.do_sh, a.do_sn, p.B, p.H, p.n, p.dv, p.dtype, delta, stream);
   };
   rc = part_delta(p.levels);
@@ -183,10 +245,8 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
   if (rc != HA_OK) return rc;
   for (int l = p.levels - 1; l >= 0; --l) {
     const int span = p.n >> l, m = span / 2;
-    if (p.keep_parts) {
-      rc = part_delta(l);
-      if (rc != HA_OK) return rc;
-    }
+    rc = part_delta(l);
+    if (rc != HA_OK) return rc;
     a.mode = HA_MODE_HYPER;
     a.flags = p.flags & (HA_FLAG_SMOOTH | HA_FLAG_BWD_REF_SMOOTH | HA_FLAG_FORCE_SIMT);
     a.segs_per_head = 1 << l;

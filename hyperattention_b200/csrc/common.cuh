@@ -176,6 +176,71 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+
+// Waits for this thread's outstanding tcgen05.ld; the loaded registers are passed through the statement so that
+// no use of them can be scheduled ahead of the wait.
+__device__ __forceinline__ void tmem_ld_fence(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+                 "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+// Packed pairs of fp32 (sm_100 executes fma/add/mul on two floats per instruction)
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack_u2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+
+// Optional per-phase cycle counters of the attention kernels (compiled in only with -DHA_PHASE_TIMING; the counters
+// of the first CTAs are written to the buffer registered with ha_debug_set_timing_buffer_fwd / _bwd).
+#ifdef HA_PHASE_TIMING
+static __device__ unsigned long long* g_timing_buf = nullptr;   // one per translation unit
+#define HA_T_SETTER(name) extern "C" int name(void* buf) { return cudaMemcpyToSymbol(::ha::g_timing_buf, &buf, sizeof(buf)) == cudaSuccess ? 0 : -4; }
+#define HA_T_DECL(n) long long _t_acc[n] = {0}; long long _t_last = clock64();
+#define HA_T_MARK(i) { long long _t_now = clock64(); _t_acc[i] += _t_now - _t_last; _t_last = _t_now; }
+#define HA_T_DUMP(n, cta, cond) if ((cond) && g_timing_buf && (cta) < 4096) { for (int _i = 0; _i < n; ++_i) g_timing_buf[(cta) * 16 + _i] = _t_acc[_i]; }
+#else
+#define HA_T_SETTER(name)
+#define HA_T_DECL(n)
+#define HA_T_MARK(i)
+#define HA_T_DUMP(n, cta, cond)
+#endif
+
+// pulls the 128-byte line holding `p` into L2 without blocking the thread
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -3,6 +3,7 @@
 
 #include <mutex>
 #include <string>
+#include <type_traits>
 
 namespace ha {
 
@@ -120,6 +121,114 @@ __global__ void __launch_bounds__(256) lsh_hash_vec_kernel(const T* __restrict__
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Angular LSH for 16-bit inputs on the tensor cores (mma.sync m16n8k16, fp32 accumulate; products of two bf16/fp16
+// values are exact in fp32, so the result equals an fp32 dot product up to summation order).  A warp takes 16 rows at
+// a time; thread (g = lane/4, t = lane%4) reads 16 bytes of rows g and g+8 per 32-column chunk and feeds them to two
+// MMAs as the A fragment.  The MMA's k index is only a summation label, so instead of shuffling the 16 bytes into
+// the canonical fragment order, the projection rows are permuted once, at kernel start, into the matching order of
+// the B fragment (8 registers per 64 columns, resident for the whole kernel).  N = 8 projections per MMA; a second
+// set of B fragments covers projections 8..15.  Sign bits come out of four ballots per 16 rows.
+// Per 16 rows and 64 columns: 4 x LDG.128 per thread, 4 MMAs, 4 ballots -> HBM-bound.
+// ---------------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]);
+template <> __device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+template <> __device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__device__ __forceinline__ uint32_t spread4(uint32_t x) {   // bit i -> bit 2i, i < 4
+  return (x & 1u) | ((x & 2u) << 1) | ((x & 4u) << 2) | ((x & 8u) << 3);
+}
+
+// CH = d / 32 column chunks; NSET = 1 (r <= 8) or 2 (r <= 16)
+template <typename T, int CH, int NSET, int UNROLL>
+__global__ void __launch_bounds__(256) lsh_hash_mma_kernel(const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int n,
+                                                           const float* __restrict__ proj, int r, int32_t* __restrict__ codes,
+                                                           long long total_rows) {
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  // B fragments: for chunk c, MMA m (0/1), register j (0/1): projection column (set*8 + g), rows c*32 + 8t + 4m + 2j + {0,1}
+  uint32_t bf[NSET][CH][2][2];
+#pragma unroll
+  for (int set = 0; set < NSET; ++set)
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int col = set * 8 + g;
+          const int row = c * 32 + 8 * t + 4 * m + 2 * j;
+          const float lo = col < r ? proj[row * r + col] : 0.f;
+          const float hi = col < r ? proj[(row + 1) * r + col] : 0.f;
+          bf[set][c][m][j] = pack2<T>(lo, hi);
+        }
+  const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long step = 16LL * UNROLL;
+  for (long long base = warp_id * step; base < total_rows; base += n_warps * step) {
+    uint4 v[UNROLL][2][CH];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int hrow = 0; hrow < 2; ++hrow) {
+        const long long row = base + u * 16 + g + 8 * hrow;
+        const bool ok = row < total_rows;
+        const long long bh = ok ? row / n : 0;
+        const int i = ok ? (int)(row - bh * n) : 0;
+        const T* p = x + (bh / H) * sb + (bh % H) * sh + (long long)i * sn + 8 * t;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) v[u][hrow][c] = ok ? __ldg(reinterpret_cast<const uint4*>(p + 32 * c)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      uint32_t code_lo = 0, code_hi = 0;   // codes of rows g and g+8
+#pragma unroll
+      for (int set = 0; set < NSET; ++set) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          const uint4 lo = v[u][0][c], hi = v[u][1][c];
+          const uint32_t a0[4] = {lo.x, hi.x, lo.y, hi.y};   // k-slots {2t,2t+1} and {2t+8,2t+9} of rows g / g+8
+          const uint32_t a1[4] = {lo.z, hi.z, lo.w, hi.w};
+          mma16816<T>(acc, a0, bf[set][c][0]);
+          mma16816<T>(acc, a1, bf[set][c][1]);
+        }
+        // acc[0], acc[1]: row g, projections 2t, 2t+1;  acc[2], acc[3]: row g+8
+        const uint32_t b0 = __ballot_sync(0xffffffffu, acc[0] > 0.f), b1 = __ballot_sync(0xffffffffu, acc[1] > 0.f);
+        const uint32_t b2 = __ballot_sync(0xffffffffu, acc[2] > 0.f), b3 = __ballot_sync(0xffffffffu, acc[3] > 0.f);
+        const int sh4 = 4 * g;
+        code_lo |= (spread4((b0 >> sh4) & 0xFu) | (spread4((b1 >> sh4) & 0xFu) << 1)) << (8 * set);
+        code_hi |= (spread4((b2 >> sh4) & 0xFu) | (spread4((b3 >> sh4) & 0xFu) << 1)) << (8 * set);
+      }
+      if (t == 0) {
+        const long long row = base + u * 16 + g;
+        if (row < total_rows) codes[row] = (int32_t)(code_lo ^ (code_lo >> 1));
+        if (row + 8 < total_rows) codes[row + 8] = (int32_t)(code_hi ^ (code_hi >> 1));
+      }
+    }
+  }
+}
+
+template <typename T, int CH>
+static void launch_hash_mma(const T* x, int64_t sb, int64_t sh, int64_t sn, int H, int n, const float* proj, int r, int32_t* codes,
+                            long long total, cudaStream_t st) {
+  constexpr int UNROLL = CH <= 2 ? 4 : 2;
+  const long long rows_per_cta = 8LL * 16 * UNROLL;
+  long long want = (total + rows_per_cta - 1) / rows_per_cta;
+  const int grid = (int)(want < 148LL * 8 ? want : 148LL * 8);
+  if (r <= 8)
+    lsh_hash_mma_kernel<T, CH, 1, UNROLL><<<grid, 256, 0, st>>>(x, sb, sh, sn, H, n, proj, r, codes, total);
+  else
+    lsh_hash_mma_kernel<T, CH, 2, UNROLL><<<grid, 256, 0, st>>>(x, sb, sh, sn, H, n, proj, r, codes, total);
+}
+
 // Generic path (any d <= 256, any element alignment): one warp per row, lane-strided elements.
 template <typename T>
 __global__ void __launch_bounds__(256) lsh_hash_generic_kernel(const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int n,
@@ -164,10 +273,21 @@ static int launch_hash(const void* x, int64_t sb, int64_t sh, int64_t sn, int B,
   if (total == 0) return HA_OK;
   constexpr int EPC = Vec16<T>::N;
   const int lpr = d / EPC;
-  const bool vec_ok = (d % EPC == 0) && (lpr == 8 || lpr == 16 || lpr == 32) && (sb % EPC == 0) && (sh % EPC == 0) &&
+  const bool vec_ok = (d % EPC == 0) && (lpr == 4 || lpr == 8 || lpr == 16 || lpr == 32) && (sb % EPC == 0) && (sh % EPC == 0) &&
                       (sn % EPC == 0) && ((uintptr_t)x % 16 == 0);
   int sms = 148;
-  if (vec_ok) {
+  if constexpr (!std::is_same<T, float>::value) {
+    // tensor-core path: 16-byte aligned rows, d a multiple of 32 up to 128.  The projection is rounded to the input
+    // dtype, which is the dtype the reference requires it to have (src/angular_lsh_triton.py:104).
+    if (vec_ok && (d == 32 || d == 64 || d == 128)) {
+      if (d == 32) launch_hash_mma<T, 1>((const T*)x, sb, sh, sn, H, n, proj, r, codes, total, st);
+      else if (d == 64) launch_hash_mma<T, 2>((const T*)x, sb, sh, sn, H, n, proj, r, codes, total, st);
+      else launch_hash_mma<T, 4>((const T*)x, sb, sh, sn, H, n, proj, r, codes, total, st);
+      HA_LAUNCHED("ha_lsh_hash");
+      return HA_OK;
+    }
+  }
+  if (vec_ok && lpr >= 8) {
     const int rows_per_cta = 8 * (32 / lpr) * 4;
     long long want = (total + rows_per_cta - 1) / rows_per_cta;
     int grid = (int)(want < (long long)sms * 8 ? want : (long long)sms * 8);
@@ -231,6 +351,61 @@ __global__ void __launch_bounds__(256) delta_kernel(const T* __restrict__ o, int
     for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     if (lane == 0) delta[row] = s;
   }
+}
+
+
+// delta, vectorised: rows of dv elements read as 16-byte chunks, LPR = dv*sizeof(T)/16 lanes per row.
+template <typename T>
+__global__ void __launch_bounds__(256) delta_vec_kernel(const T* __restrict__ o, int64_t osb, int64_t osh, int64_t osn, const T* __restrict__ go,
+                                                        int64_t gsb, int64_t gsh, int64_t gsn, int H, int n, int lpr, float* __restrict__ delta,
+                                                        long long total_rows) {
+  constexpr int EPC = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int rpw = 32 / lpr, chunk = lane % lpr, sub = lane / lpr;
+  const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  constexpr int UN = 4;
+  for (long long base = warp_id * rpw * UN; base < total_rows; base += n_warps * rpw * UN) {
+    uint4 a[UN], b[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const long long row = base + u * rpw + sub;
+      a[u] = b[u] = make_uint4(0, 0, 0, 0);
+      if (row < total_rows) {
+        const long long bh = row / n;
+        const int i = (int)(row - bh * n);
+        a[u] = __ldg(reinterpret_cast<const uint4*>(o + (bh / H) * osb + (bh % H) * osh + (long long)i * osn + chunk * EPC));
+        b[u] = __ldg(reinterpret_cast<const uint4*>(go + (bh / H) * gsb + (bh % H) * gsh + (long long)i * gsn + chunk * EPC));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      float fa[EPC], fb[EPC];
+      unpack16<T>(a[u], fa);
+      unpack16<T>(b[u], fb);
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPC; ++e) s = fmaf(fa[e], fb[e], s);
+      for (int off = lpr >> 1; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+      const long long row = base + u * rpw + sub;
+      if (chunk == 0 && row < total_rows) delta[row] = s;
+    }
+  }
+}
+
+template <typename T>
+static bool launch_delta_vec(const void* o, int64_t osb, int64_t osh, int64_t osn, const void* go, int64_t gsb, int64_t gsh, int64_t gsn,
+                             int H, int n, int dv, float* delta, long long rows, cudaStream_t st) {
+  constexpr int EPC = Vec16<T>::N;
+  const int lpr = dv / EPC;
+  const bool ok = dv % EPC == 0 && (lpr == 2 || lpr == 4 || lpr == 8 || lpr == 16 || lpr == 32) && osb % EPC == 0 && osh % EPC == 0 &&
+                  osn % EPC == 0 && gsb % EPC == 0 && gsh % EPC == 0 && gsn % EPC == 0 && (uintptr_t)o % 16 == 0 && (uintptr_t)go % 16 == 0;
+  if (!ok) return false;
+  const long long per_cta = 8LL * (32 / lpr) * 4;
+  long long want = (rows + per_cta - 1) / per_cta;
+  const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
+  delta_vec_kernel<T><<<grid, 256, 0, st>>>((const T*)o, osb, osh, osn, (const T*)go, gsb, gsh, gsn, H, n, lpr, delta, rows);
+  return true;
 }
 
 template <typename T>
@@ -344,6 +519,17 @@ int ha_delta(const void* o, int64_t osb, int64_t osh, int64_t osn, const void* g
   cudaStream_t st = (cudaStream_t)stream;
   const long long rows = (long long)B * H * n;
   if (rows == 0) return HA_OK;
+  bool done = false;
+  switch (dtype) {
+    case HA_BF16: done = launch_delta_vec<__nv_bfloat16>(o, osb, osh, osn, go, gsb, gsh, gsn, H, n, dv, delta, rows, st); break;
+    case HA_FP16: done = launch_delta_vec<__half>(o, osb, osh, osn, go, gsb, gsh, gsn, H, n, dv, delta, rows, st); break;
+    case HA_FP32: done = launch_delta_vec<float>(o, osb, osh, osn, go, gsb, gsh, gsn, H, n, dv, delta, rows, st); break;
+    default: return HA_ERR_DTYPE;
+  }
+  if (done) {
+    HA_LAUNCHED("ha_delta");
+    return HA_OK;
+  }
   const int grid = grid_for(rows, 8);
   switch (dtype) {
     case HA_BF16: delta_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)o, osb, osh, osn, (const __nv_bfloat16*)go, gsb, gsh, gsn, H, n, dv, delta, rows); break;
