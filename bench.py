@@ -31,7 +31,7 @@ BLOCK, SAMPLE, MIN_SEQ, BITS = 256, 256, 2048, 8
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200', choices=['b200', 'reference'])
     ap.add_argument('--workload', default='c1', choices=['c1', 'c2'])
@@ -123,28 +123,38 @@ def timed(fn, steps, warmup, sync_all):
     return e0.elapsed_time(e1) / steps
 
 
-def cpu_baseline(workload, n, d, heads_sample, total_heads, seed):
+def cpu_baseline(workload, n, d, heads_sample, total_heads, seed, target_seconds=12.0):
     """The reference's host-side path restated on the CPU (oracle): its glue, hash, stable sort and merge, with the two
-    device-only attention callables replaced by the oracle's PyTorch Functions.  Timed on `heads_sample` heads and
-    scaled linearly to `total_heads`."""
+    device-only attention callables replaced by the oracle's PyTorch Functions.  Timed on a sample of heads (one head
+    first; if that is quick, as many heads as fit in about `target_seconds`) and scaled linearly to `total_heads`."""
     from oracle import hyper_oracle as O
-    q, k, v, do = clustered_inputs(heads_sample, n, d, seed, dtype=torch.float32)
     g = torch.Generator().manual_seed(1234)
     proj = torch.randn(1, 1, d, BITS, generator=g)
-    orc = O.HyperAttentionOracle(proj, BLOCK, SAMPLE, MIN_SEQ, False)
-    q, k, v = [t.requires_grad_() for t in (q, k, v)]
-    t0 = time.perf_counter()
-    o = orc(q, k, v, causal=(workload == 'c2'))
-    t1 = time.perf_counter()
-    o.backward(do)
-    t2 = time.perf_counter()
-    scale = total_heads / heads_sample
-    sec = (t2 - t0) * scale
+
+    def run(hs):
+        q, k, v, do = clustered_inputs(hs, n, d, seed, dtype=torch.float32)
+        orc = O.HyperAttentionOracle(proj, BLOCK, SAMPLE, MIN_SEQ, False)
+        q, k, v = [t.requires_grad_() for t in (q, k, v)]
+        t0 = time.perf_counter()
+        o = orc(q, k, v, causal=(workload == 'c2'))
+        t1 = time.perf_counter()
+        o.backward(do)
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1
+
+    hs = max(1, heads_sample)
+    f, b = run(hs)
+    if heads_sample <= 1 and (f + b) < target_seconds / 2:
+        hs = int(max(1, min(total_heads, target_seconds // max(f + b, 1e-3))))
+        if hs > 1:
+            f, b = run(hs)
+    scale = total_heads / hs
+    sec = (f + b) * scale
     return {'value': n / sec, 'unit': 'tokens/s', 'cores': torch.get_num_threads(), 'kind': 'port',
-            'sample': f'{heads_sample} of {total_heads} heads at n={n}, fp32, fwd {t1 - t0:.2f}s + bwd {t2 - t1:.2f}s, scaled x{scale:g} '
+            'sample': f'{hs} of {total_heads} heads at n={n}, fp32, fwd {f:.2f}s + bwd {b:.2f}s, scaled x{scale:g} '
                       f'(reference glue/hash/sort/merge restated in PyTorch; attention kernels restated because the '
                       f'reference has none for CPU)',
-            'host_cpus': os.cpu_count(), 'fwd_s_scaled': (t1 - t0) * scale, 'fwd_bwd_s_scaled': sec}
+            'host_cpus': os.cpu_count(), 'fwd_s_scaled': f * scale, 'fwd_bwd_s_scaled': sec, 'heads_sampled': hs}
 
 
 def main():
@@ -167,7 +177,7 @@ def main():
         cb = cpu_baseline(args.workload, n, d, args.cpu_heads, heads, seed)
         vals = [cb['value']]
         for _ in range(max(0, args.steps - 1)):
-            vals.append(cpu_baseline(args.workload, n, d, args.cpu_heads, heads, seed)['value'])
+            vals.append(cpu_baseline(args.workload, n, d, cb['heads_sampled'], heads, seed)['value'])
         val = sum(vals) / len(vals)
         cb['value'] = val
         line = {'impl': 'reference', 'metric': 'hyperattention_fwd_bwd_tokens_per_s', 'value': val, 'unit': 'tokens/s', 'n_gpus': args.gpus,
@@ -196,7 +206,8 @@ def main():
 
     # same data on every world size: generate all heads on the host, keep this rank's slice
     host = clustered_inputs(heads, n, d, seed)
-    host = [t[:, rank * hpg:(rank + 1) * hpg].contiguous().pin_memory() for t in host]
+    from hyperattention_b200.partition import shard_heads
+    host = [shard_heads(t, rank, world).contiguous().pin_memory() for t in host]
     q, k, v, do = [t.to(dev) for t in host]
     q, k, v = [t.requires_grad_() for t in (q, k, v)]
     gen = torch.Generator().manual_seed(1234)
@@ -219,7 +230,6 @@ def main():
     l0 = ha.launch_count()
     ms = timed(fwd_bwd, args.steps, args.warmup, sync_all)
     launches = (ha.launch_count() - l0) // (args.steps + args.warmup) * args.steps
-    clocks = sampler.stop()
     ms_fwd = timed(fwd, args.steps, args.warmup, sync_all)
     if dist is not None:
         t = torch.tensor([ms, ms_fwd], device=dev)
@@ -240,6 +250,7 @@ def main():
         t = torch.tensor([ms_e2e], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = t.item()
+    clocks = sampler.stop()
     bytes_io = sum(t.numel() * t.element_size() for t in host)
 
     line = {'metric': 'hyperattention_fwd_bwd_tokens_per_s', 'value': n / (ms * 1e-3), 'unit': 'tokens/s', 'n_gpus': world,
@@ -258,8 +269,16 @@ def main():
         dist.destroy_process_group()
 
 
+# DRAM traffic of one launch of the dominant kernel (attn_tc_bwd_kernel, hyper pattern), from an ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum) of the 8-head x 65536-token case, which scales linearly with the
+# number of rows (fixed work per row): 765.0 MB read + 407.8 MB written for 524288 rows.  Summary of the capture:
+# profiles/attn_tc_bwd_kernel_hyper_8x65536.md.
+BWD_DRAM_BYTES_PER_ROW = 2237.0
+
+
 def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
-    """roofline of the dominant kernel (timed alone, CUDA events), the exact-flash comparator, the CPU baseline."""
+    """Kernel-alone timings and rooflines (CUDA events on the launching stream), the exact-flash comparator, the causal
+    configuration's times, the CPU baseline."""
     from hyperattention_b200 import ops
     peaks = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'src': 'fallback'}
     pk = os.path.join(ROOT, 'MEASURED_PEAKS.json')
@@ -269,44 +288,73 @@ def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
     sync = torch.cuda.synchronize
     out = {}
     rows = hpg * n
+    T = lambda t: t.transpose(1, 2)
     with torch.no_grad():
         qd, kd, vd = q.detach(), k.detach(), v.detach()
         proj = mod.lsh.proj_f32()
-        # stage timings of one non-causal call over this rank's heads
         t_hash = timed(lambda: ops.lsh_hash(qd, proj), 10, 3, sync)
         codes = ops.lsh_hash(qd, proj)
         t_sort = timed(lambda: ops.seg_sort(codes, BITS), 10, 3, sync)
         qi = ops.seg_sort(codes, BITS).view(1, hpg, n)
         ki = ops.seg_sort(ops.lsh_hash(kd, proj), BITS).view(1, hpg, n)
-        T = lambda t: t.transpose(1, 2)
-        t_attn = timed(lambda: ops.hyper_attn_func(T(qd), T(kd), T(vd), T(qi), T(ki), BLOCK, SAMPLE), 10, 3, sync)
-        flops = 4.0 * (BLOCK + SAMPLE) * d * rows
-        out['stages_ms'] = {'lsh_hash_per_tensor': t_hash, 'seg_sort_per_tensor': t_sort, 'hyper_attn_fwd': t_attn}
-        out['stage_rooflines'] = {
-            'lsh_hash': {'bound': 'hbm', 'achieved': rows * (d * 2 + 4) / t_hash / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
-            'seg_sort': {'bound': 'hbm', 'achieved': rows * 8 / t_sort / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
-            'hyper_attn_fwd_hbm': {'bound': 'hbm', 'achieved': rows * (4 * d * 2 + 12) / t_attn / 1e6, 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
-        }
-        for r_ in out['stage_rooflines'].values():
-            r_['frac'] = r_['achieved'] / r_['peak']
-        ach = flops / (t_attn * 1e-3) / 1e12
-        out['roofline'] = {'bound': 'tensor', 'kernel': 'attn_tc_fwd_kernel (hyper pattern, forward)', 'achieved': ach,
-                           'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s', 'frac': ach / peaks['bf16_tflops'], 'traffic': None,
-                           'peak_source': peaks['src'], 'launch_ms': t_attn,
-                           'algorithmic_flops_per_launch': flops}
-        # exact attention of the same shape: our sm_100a flash kernel and the library kernel behind torch SDPA
+        t_gather = timed(lambda: ops.indexing(qd, qi), 10, 3, sync)
+        t_fwd = timed(lambda: ops.hyper_attn_func(T(qd), T(kd), T(vd), T(qi), T(ki), BLOCK, SAMPLE), 10, 3, sync)
+        o, lse = ops.hyper_attn_func(T(qd), T(kd), T(vd), T(qi), T(ki), BLOCK, SAMPLE)
+        # the backward kernel alone: delta and the zeroed accumulators are prepared outside the timed launches
+        qi32, ki32 = qi.view(hpg, n).contiguous(), ki.view(hpg, n).contiguous()
+        delta = (o.float() * T(do).float()).sum(-1).transpose(1, 2).contiguous()
+        acc = torch.zeros(rows * 3 * d, dtype=torch.float32, device=dev)
+        bwd = lambda: ops.hyper_bwd_launch(T(qd), T(kd), T(vd), qi32, ki32, None, o, lse, T(do), delta, acc, BLOCK, SAMPLE, d ** -0.5, 0)
+        t_bwd = timed(bwd, 10, 3, sync)
+        del acc, delta
+    fl_fwd = 4.0 * (BLOCK + SAMPLE) * d * rows
+    fl_bwd = 10.0 * (BLOCK + SAMPLE) * d * rows
+    tf = lambda fl, ms: fl / (ms * 1e-3) / 1e12
+    gbs = lambda by, ms: by / (ms * 1e-3) / 1e9
+    out['kernels_ms'] = {'lsh_hash_per_tensor': t_hash, 'seg_sort_per_tensor': t_sort, 'gather_rows_per_tensor': t_gather,
+                         'attn_tc_fwd_kernel': t_fwd, 'attn_tc_bwd_kernel': t_bwd}
+    st = {
+        'lsh_hash': {'bound': 'hbm', 'achieved': gbs(rows * (d * 2 + 4), t_hash), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
+        'seg_sort': {'bound': 'hbm', 'achieved': gbs(rows * 8, t_sort), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
+        'gather_rows': {'bound': 'hbm', 'achieved': gbs(rows * (2 * d * 2 + 4), t_gather), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
+        'attn_tc_fwd_kernel': {'bound': 'tensor', 'achieved': tf(fl_fwd, t_fwd), 'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s'},
+        'attn_tc_fwd_kernel_hbm': {'bound': 'hbm', 'achieved': gbs(rows * (4 * d * 2 + 12), t_fwd), 'peak': peaks['hbm_gbs'], 'unit': 'GB/s'},
+    }
+    for r_ in st.values():
+        r_['frac'] = r_['achieved'] / r_['peak']
+    out['stage_rooflines'] = st
+    ach = tf(fl_bwd, t_bwd)
+    out['roofline'] = {'bound': 'tensor', 'kernel': 'attn_tc_bwd_kernel (hyper pattern; the longest kernel of the step)', 'achieved': ach,
+                       'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s', 'frac': ach / peaks['bf16_tflops'],
+                       'traffic': BWD_DRAM_BYTES_PER_ROW * rows if BWD_DRAM_BYTES_PER_ROW else None,
+                       'peak_source': peaks['src'], 'launch_ms': t_bwd, 'algorithmic_flops_per_launch': fl_bwd,
+                       'algorithmic_bytes_per_launch': rows * (8 * d * 2 + 16)}
+    # the causal configuration (BASELINE config 2) on the same tensors: times do not depend on the values
+    def c_fwd():
+        with torch.no_grad():
+            return mod(q, k, v, causal=True)
+    def c_fwd_bwd():
+        oo = mod(q, k, v, causal=True)
+        return torch.autograd.grad(oo, (q, k, v), do)
+    c_fwd_bwd()
+    tc_fb = timed(c_fwd_bwd, 5, 2, sync)
+    tc_f = timed(c_fwd, 5, 2, sync)
+    out['causal_config2'] = {'fwd_ms': tc_f, 'fwd_bwd_ms': tc_fb, 'fwd_bwd_tokens_per_s': n / (tc_fb * 1e-3)}
+    # exact attention of the same shape: our sm_100a flash kernel and the library kernel behind torch SDPA
+    with torch.no_grad():
         t_ours = timed(lambda: ops.flash_attn_func(T(qd), T(kd), T(vd), None, True), 2, 1, sync)
-        out['exact_flash'] = {'ours_causal_fwd_ms': t_ours, 'ours_causal_fwd_tflops': 2.0 * n * n * d * hpg / (t_ours * 1e-3) / 1e12}
+    out['exact_flash'] = {'ours_causal_fwd_ms': t_ours, 'ours_causal_fwd_tflops': 2.0 * n * n * d * hpg / (t_ours * 1e-3) / 1e12}
     try:
         import torch.nn.functional as F
         qs, ks, vs = [t.detach().clone().requires_grad_() for t in (q, k, v)]
         f = lambda: F.scaled_dot_product_attention(qs, ks, vs, is_causal=True)
         t_f = timed(lambda: f(), 2, 1, sync)
         def fb():
-            o = f()
-            torch.autograd.grad(o, (qs, ks, vs), do)
+            oo = f()
+            torch.autograd.grad(oo, (qs, ks, vs), do)
         t_fb = timed(fb, 2, 1, sync)
-        out['exact_flash'].update({'sdpa_causal_fwd_ms': t_f, 'sdpa_causal_fwd_bwd_ms': t_fb})
+        out['exact_flash'].update({'sdpa_causal_fwd_ms': t_f, 'sdpa_causal_fwd_bwd_ms': t_fb,
+                                   'causal_fwd_speedup_vs_sdpa': t_f / tc_f, 'causal_fwd_bwd_speedup_vs_sdpa': t_fb / tc_fb})
         del qs, ks, vs
     except Exception as e:   # the comparator is informative only
         out['exact_flash']['sdpa_error'] = str(e)[:200]

@@ -186,6 +186,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row);
   const int krow = me.krow, qt_first = me.qt_first, qt_count = me.qt_count, k_tile = me.k_tile;
   if (qt_count <= 0) return;     // uniform over the CTA; nothing allocated yet
+  if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
 
   const uint32_t bar = smem_u32(&mma_bar);
   if (tid == 0) {

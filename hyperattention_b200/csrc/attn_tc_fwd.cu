@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   const SegInfo si = seg_info(p, seg);
   const uint32_t bar = smem_u32(&mma_bar);
 
+  if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
   if (tid == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();

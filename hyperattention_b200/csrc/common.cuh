@@ -11,7 +11,7 @@
 namespace ha {
 
 constexpr int TILE = 128;           // rows per attention tile (the reference's BLOCK_M = BLOCK_N)
-constexpr int SPIN_LIMIT = 1 << 22;  // iteration cap of every device-side wait
+constexpr int SPIN_LIMIT = 1 << 18;  // poll cap of every device-side wait (a legitimate wait is a few microseconds)
 
 extern std::atomic<long long> g_launches;
 void set_cuda_error(cudaError_t e, const char* where);

@@ -28,6 +28,27 @@ def _ptr(t):
     return C.c_void_p(t.data_ptr()) if t is not None else None
 
 
+_STATUS = {}
+
+
+def _status_word(device):
+    """One int32 per device that the kernels set when a bounded device-side wait expires (0 = healthy)."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=f'cuda:{key}')
+    return _STATUS[key]
+
+
+def check_device_status(device=None, reset=True):
+    """Synchronises and raises if a kernel reported a timeout since the last check."""
+    w = _status_word(device if device is not None else torch.cuda.current_device())
+    v = int(w.item())
+    if v != 0:
+        if reset:
+            w.zero_()
+        raise RuntimeError(f'hyperattention_b200: device-side wait timed out (status {v})')
+
+
 def _cuda(*ts):
     for t in ts:
         assert t is not None and t.is_cuda, 'tensors must be CUDA tensors (there is no CPU implementation)'
@@ -167,6 +188,7 @@ class HyperAttnFunc(torch.autograd.Function):
         p.o = _ptr(o)
         p.o_sb, p.o_sh, p.o_sn = _bhn(o)
         p.lse = _ptr(lse)
+        p.status = _ptr(_status_word(q.device))
         with torch.cuda.device(q.device):
             rc = L.load().ha_attn_fwd(C.byref(p), _stream())
         L.check(rc, 'ha_attn_fwd')
@@ -184,29 +206,39 @@ class HyperAttnFunc(torch.autograd.Function):
         dv = v.shape[-1]
         dev = q.device
         acc = torch.zeros(B * H * n * (2 * d + dv), dtype=torch.float32, device=dev)
-        dq_acc, dk_acc, dv_acc = acc[:B * H * n * d], acc[B * H * n * d:2 * B * H * n * d], acc[2 * B * H * n * d:]
         delta = torch.empty(B, H, n, dtype=torch.float32, device=dev)
         lib = L.load()
         with torch.cuda.device(dev):
             rc = lib.ha_delta(_ptr(o), *_bhn(o), _ptr(do), *_bhn(do), B, H, n, dv, _dtype_id(q), _ptr(delta), _stream())
             L.check(rc, 'ha_delta')
-            p = L.AttnParams()
-            p.mode, p.dtype, p.flags = L.MODE_HYPER, _dtype_id(q), flags
-            p.B, p.H, p.n, p.d, p.dv = B, H, n, d, dv
-            p.segs_per_head, p.span, p.q_off, p.k_off, p.m_q, p.m_k = 1, n, 0, 0, n, n
-            p.block_size, p.sample_size, p.scale = block_size, sample_size, scale
-            _fill_qkv(p, q, k, v)
-            p.q_idx, p.k_idx, p.sample_idx = _ptr(qi), _ptr(ki), _ptr(si) if has_si else None
-            p.o = _ptr(o)
-            p.o_sb, p.o_sh, p.o_sn = _bhn(o)
-            p.lse = _ptr(lse)
-            p.d_o = _ptr(do)
-            p.do_sb, p.do_sh, p.do_sn = _bhn(do)
-            p.delta, p.dq_acc, p.dk_acc, p.dv_acc = _ptr(delta), _ptr(dq_acc), _ptr(dk_acc), _ptr(dv_acc)
-            rc = lib.ha_attn_bwd(C.byref(p), _stream())
-            L.check(rc, 'ha_attn_bwd')
+            hyper_bwd_launch(q, k, v, qi, ki, si if has_si else None, o, lse, do, delta, acc, block_size, sample_size, scale, flags)
             grads = _cast_grads(lib, acc, q.dtype, B, H, n, d, dv)
         return grads + (None,) * 8
+
+
+def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sample_size, scale, flags):
+    """One ha_attn_bwd call (HA_MODE_HYPER) on [B, n, H, *] views; acc = zeroed fp32 buffer holding dq | dk | dv
+    accumulators ([B,H,n,d], [B,H,n,d], [B,H,n,dv] back to back).  Nothing else is launched."""
+    B, n, H, d = q.shape
+    dv = v.shape[-1]
+    r = B * H * n
+    p = L.AttnParams()
+    p.mode, p.dtype, p.flags = L.MODE_HYPER, _dtype_id(q), flags
+    p.B, p.H, p.n, p.d, p.dv = B, H, n, d, dv
+    p.segs_per_head, p.span, p.q_off, p.k_off, p.m_q, p.m_k = 1, n, 0, 0, n, n
+    p.block_size, p.sample_size, p.scale = block_size, sample_size, scale
+    _fill_qkv(p, q, k, v)
+    p.q_idx, p.k_idx, p.sample_idx = _ptr(qi), _ptr(ki), _ptr(si)
+    p.o = _ptr(o)
+    p.o_sb, p.o_sh, p.o_sn = _bhn(o)
+    p.lse = _ptr(lse)
+    p.d_o = _ptr(do)
+    p.do_sb, p.do_sh, p.do_sn = _bhn(do)
+    p.delta = _ptr(delta)
+    p.dq_acc, p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr()), C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
+    p.status = _ptr(_status_word(q.device))
+    rc = L.load().ha_attn_bwd(C.byref(p), _stream())
+    L.check(rc, 'ha_attn_bwd')
 
 
 def _cast_grads(lib, acc, dtype, B, H, n, d, dv):
@@ -300,6 +332,7 @@ def _flash_params(q, k, v, o, lse, causal, scale, flags):
     p.o = _ptr(o)
     p.o_sb, p.o_sh, p.o_sn = _bhn(o)
     p.lse = _ptr(lse)
+    p.status = _ptr(_status_word(q.device))
     return p
 
 
@@ -331,6 +364,7 @@ class CausalHyperFunc(torch.autograd.Function):
         p.keep_parts = 1 if (grad_reference and need_grad) else 0
         p.scale = scale
         p.q, p.k, p.v, p.proj, p.o, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(proj_f32), _ptr(o), _ptr(lse)
+        p.status = _ptr(_status_word(dev))
         lib = L.load()
         saved_bytes = lib.ha_causal_saved_bytes(C.byref(p))
         scratch_bytes = lib.ha_causal_scratch_bytes(C.byref(p), 0)
@@ -362,6 +396,7 @@ class CausalHyperFunc(torch.autograd.Function):
         p.keep_parts, p.scale = keep_parts, scale
         p.q, p.k, p.v, p.proj, p.o, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(proj_f32), _ptr(o), _ptr(lse)
         p.saved, p.saved_bytes = _ptr(saved), saved.numel()
+        p.status = _ptr(_status_word(dev))
         lib = L.load()
         scratch_bytes = lib.ha_causal_scratch_bytes(C.byref(p), 1)
         scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=dev)

@@ -17,3 +17,14 @@ def pytest_configure(config):
 @pytest.fixture(scope='session')
 def golden_dir():
     return GOLDEN
+
+
+@pytest.fixture(autouse=True)
+def _no_device_timeouts(request):
+    """After every GPU test: fail if a kernel reported that one of its bounded waits expired."""
+    yield
+    if request.node.get_closest_marker('gpu') is not None:
+        import torch
+        if torch.cuda.is_available():
+            import hyperattention_b200 as ha
+            ha.check_device_status()
