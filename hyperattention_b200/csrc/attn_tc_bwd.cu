@@ -139,8 +139,17 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
     it.qt_count = w.count / TILE;
   } else {
     const int i2 = hyper ? item - items_blk : item;
-    it.k_tile = i2 / n_chunks;
-    const int z = i2 - it.k_tile * n_chunks;
+    int z;
+    if (hyper) {
+      // the items of the sampled key tiles that cover the same chunk of query tiles are neighbours in the grid: the
+      // second one finds the query rows and the dQ rows of the chunk in L2
+      const int ns = p.sample_size / TILE;
+      z = i2 / ns;
+      it.k_tile = i2 - z * ns;
+    } else {
+      it.k_tile = i2 / n_chunks;
+      z = i2 - it.k_tile * n_chunks;
+    }
     const int kr = it.k_tile * TILE + tid;
     if (hyper) it.krow = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + kr] : kr;
     else it.krow = kr < p.m_k ? kr : -1;

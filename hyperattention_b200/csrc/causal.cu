@@ -54,19 +54,33 @@ __global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ 
   const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int dv = lpr * EPC;
-  for (long long base = warp_id * rpw; base < total_rows; base += n_warps * rpw) {
-    const long long row = base + sub;
-    const bool ok = row < total_rows;
-    const int i = ok ? (int)(row % n) : 0;
-    uint4 g = make_uint4(0, 0, 0, 0);
-    if (ok) g = __ldg(reinterpret_cast<const uint4*>(d_o + row * dv + chunk * EPC));
+  constexpr int UN = 4;   // row groups per iteration: keeps several independent loads in flight per lane
+  for (long long base = warp_id * rpw * UN; base < total_rows; base += n_warps * rpw * UN) {
+    long long row[UN];
+    bool ok[UN];
+    int i[UN];
+    uint4 g[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      row[u] = base + u * rpw + sub;
+      ok[u] = row[u] < total_rows;
+      i[u] = ok[u] ? (int)(row[u] % n) : 0;
+      g[u] = make_uint4(0, 0, 0, 0);
+      if (ok[u]) g[u] = __ldg(reinterpret_cast<const uint4*>(d_o + row[u] * dv + chunk * EPC));
+    }
     for (int part = 0; part <= levels; ++part) {
-      const bool need = ok && (part == levels || ((i / (n >> (part + 1))) & 1));
-      float s = 0.f;
-      if (need) {
-        const T* po = reinterpret_cast<const T*>(parts0 + part * part_stride_bytes) + row * dv + chunk * EPC;
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(po));
-        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
+      bool need[UN];
+      uint4 a[UN];
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        need[u] = ok[u] && (part == levels || ((i[u] / (n >> (part + 1))) & 1));
+        a[u] = make_uint4(0, 0, 0, 0);
+        if (need[u]) a[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(parts0 + part * part_stride_bytes) + row[u] * dv + chunk * EPC));
+      }
+#pragma unroll
+      for (int u = 0; u < UN; ++u) {
+        float s = 0.f;
+        const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, gw[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
           if constexpr (EPC == 8) {
@@ -77,9 +91,9 @@ __global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ 
             s = fmaf(__uint_as_float(aw[w]), __uint_as_float(gw[w]), s);
           }
         }
+        for (int off = lpr >> 1; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (need[u] && chunk == 0) delta[(long long)part * total_rows + row[u]] = s;
       }
-      for (int off = lpr >> 1; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-      if (need && chunk == 0) delta[(long long)part * total_rows + row] = s;
     }
   }
 }
@@ -215,7 +229,7 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
     const int es = dtype_size(p.dtype), epc = 16 / es, lpr = p.dv / epc;
     if (p.dv % epc == 0 && (lpr == 2 || lpr == 4 || lpr == 8 || lpr == 16 || lpr == 32) && (uintptr_t)p.d_o % 16 == 0) {
       const long long part_stride = (uint8_t*)sv.part_o(1) - (uint8_t*)sv.part_o(0);
-      const long long per_cta = 8LL * (32 / lpr);
+      const long long per_cta = 8LL * (32 / lpr) * 4;
       long long want = (pl.rows + per_cta - 1) / per_cta;
       const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
       if (p.dtype == HA_BF16)
