@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c1|c2] [--impl reference] [--seq-len n] [--heads H]
 
 A step is one forward+backward pass of the HyperAttention module over one synthetic batch of the headline shape
-(batch 1, 32 heads, head_dim 64, 131072 tokens, bf16; BASELINE config 1 = non-causal, config 2 = causal).  The
+(batch 1, 32 heads, head_dim 64, 131072 tokens, bf16; benchmark configuration 1 = non-causal, config 2 = causal).  The
 heads are partitioned over the GPUs (no collective on the data path); the time of a step is the maximum over ranks,
 measured with CUDA events.  One JSON line is printed by rank 0.
 
@@ -43,7 +43,7 @@ def parse():
 
 
 def clustered_inputs(heads, n, d, seed, device='cpu', dtype=torch.bfloat16):
-    """BASELINE configs 1/2: per head 64 unit-norm centroids shared by Q and K, per-token Gaussian noise of total norm
+    """benchmark configurations 1/2: per head 64 unit-norm centroids shared by Q and K, per-token Gaussian noise of total norm
     ~0.3, V ~ N(0,1), dO ~ N(0,1).  Seeded, generated on the CPU generator so that every rank/impl sees the same data."""
     g = torch.Generator().manual_seed(seed)
     cent = torch.randn(heads, 64, d, generator=g)
@@ -165,7 +165,7 @@ def main():
     n, d, heads = args.seq_len, DIM, args.heads
     causal = args.workload == 'c2'
     seed = 1 if args.workload == 'c1' else 2
-    config = {'workload': f"BASELINE config {'2 (causal)' if causal else '1 (non-causal)'}: batch 1, {heads} heads, head_dim {d}, "
+    config = {'workload': f"benchmark configuration {'2 (causal)' if causal else '1 (non-causal)'}: batch 1, {heads} heads, head_dim {d}, "
                           f"seq_len {n}, bf16, block 256, sample 256, lsh 8 bits" + (', min_seq_len 2048' if causal else ''),
               'step': 'forward + backward of HyperAttention.forward', 'heads_per_gpu': heads // max(world, 1),
               'partition': 'heads over GPUs, no collective', 'l2': 'inputs (4 x 537 MB per step at 1 GPU) exceed the 126 MB L2',
@@ -329,7 +329,7 @@ def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
                        'traffic': BWD_DRAM_BYTES_PER_ROW * rows if BWD_DRAM_BYTES_PER_ROW else None,
                        'peak_source': peaks['src'], 'launch_ms': t_bwd, 'algorithmic_flops_per_launch': fl_bwd,
                        'algorithmic_bytes_per_launch': rows * (8 * d * 2 + 16)}
-    # the causal configuration (BASELINE config 2) on the same tensors: times do not depend on the values
+    # the causal configuration (benchmark configuration 2) on the same tensors: times do not depend on the values
     def c_fwd():
         with torch.no_grad():
             return mod(q, k, v, causal=True)

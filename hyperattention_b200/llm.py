@@ -1,5 +1,5 @@
 """ChatGLM2-style integration of HyperAttention: the attention-layer patch of the reference and a random-init decoder of
-the ChatGLM2-6B shape to run it in (BASELINE config 4).
+the ChatGLM2-6B shape to run it in (benchmark configuration 4).
 
 * ``FastCoreAttention`` and ``patch_attention_layers`` mirror chatglm_fast_attention.py:8-70 and
   replace_llm_attention.py:6-44 of the reference: same constructor arguments, same layer-selection options, same

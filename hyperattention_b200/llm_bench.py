@@ -1,4 +1,4 @@
-"""Prefill benchmark of the ChatGLM2-6B-shaped decoder (BASELINE config 4): batch 1 x 32768 uniformly random token ids,
+"""Prefill benchmark of the ChatGLM2-6B-shaped decoder (benchmark configuration 4): batch 1 x 32768 uniformly random token ids,
 attention of the last 14 of 28 blocks replaced by HyperAttention; reports prefill tokens/s of the all-exact and the
 patched model and the deviation of the last-position logits.
 

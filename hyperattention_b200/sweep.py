@@ -1,4 +1,4 @@
-"""Sequence-length sweep (BASELINE config 3): batch 1, 32 heads, head_dim 64, bf16, i.i.d. N(0,1) inputs, causal and
+"""Sequence-length sweep (benchmark configuration 3): batch 1, 32 heads, head_dim 64, bf16, i.i.d. N(0,1) inputs, causal and
 non-causal, smooth_block off/on; each point is timed (CUDA events, median of `reps`) forward and forward+backward and
 compared with exact attention of the same shape (torch scaled_dot_product_attention).  One JSON line per point.
 

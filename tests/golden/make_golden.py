@@ -192,7 +192,7 @@ def module_cases(ref, out_dir):
                'o': o.detach().clone(), 'lse': lse.detach().clone(), 'do': do, 'dq': q.grad.clone(), 'dk': k.grad.clone(),
                'dv': v.grad.clone()}
         if tag == 'c0_noncausal':
-            # BASELINE config 0 in full.  Inputs are regenerated from the seed by the tests (q, k, v, then the
+            # benchmark configuration 0 in full.  Inputs are regenerated from the seed by the tests (q, k, v, then the
             # module's proj_dir draw, then do, all from torch.manual_seed(seed)); big outputs keep every 8th row.
             rec['q_codes'] = mod.lsh.hash_torch(q.detach()).to(torch.uint8)
             rec['k_codes'] = mod.lsh.hash_torch(k.detach()).to(torch.uint8)

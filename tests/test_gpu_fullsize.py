@@ -1,4 +1,4 @@
-"""GPU tests at the BASELINE sizes (batch 1, 32 heads, head_dim 64, 131072 tokens, bf16; configs 1 and 2).
+"""GPU tests at the headline benchmark sizes (batch 1, 32 heads, head_dim 64, 131072 tokens, bf16; configs 1 and 2).
 
 The CPU oracle is too slow for all 32 heads at this length, so full-size runs are checked through size-independent
 properties (permutation validity and stability, softmax rows summing to one, linearity in V, causality, determinism)

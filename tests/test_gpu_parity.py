@@ -273,7 +273,7 @@ def _golden_module(golden_dir, tag):
 @pytest.mark.parametrize('tag', ['c0_noncausal', 'causal_2lvl', 'causal_odd', 'short_flash', 'causal_leaf', 'smooth'])
 @pytest.mark.parametrize('fused', [True, False])
 def test_module_matches_reference_golden(ha, golden_dir, tag, fused):
-    """float32, the reference's own HyperAttention.forward output and gradients (BASELINE config 0 is 'c0_noncausal')"""
+    """float32, the reference's own HyperAttention.forward output and gradients (benchmark configuration 0 is 'c0_noncausal')"""
     r = _golden_module(golden_dir, tag)
     mod = _module_pair(ha, r, fused_causal=fused)
     q, k, v = [dev(r[x]).requires_grad_() for x in 'qkv']
@@ -287,7 +287,7 @@ def test_module_matches_reference_golden(ha, golden_dir, tag, fused):
     assert rel(q.grad[:, :, ::st], r['dq']) < 2e-4
     assert rel(k.grad[:, :, ::st], r['dk']) < 2e-4
     assert rel(v.grad[:, :, ::st], r['dv']) < 2e-4
-    if 'q_codes' in r:   # bit-exact integer stages of BASELINE config 0
+    if 'q_codes' in r:   # bit-exact integer stages of benchmark configuration 0
         qc = mod.lsh.hash_triton(q.detach())
         kc = mod.lsh.hash_triton(k.detach())
         assert torch.equal(qc.cpu(), r['q_codes'].int()) and torch.equal(kc.cpu(), r['k_codes'].int())

@@ -71,7 +71,7 @@ def test_flash_matches_reference_kernel(golden_dir, tag):
 def _module_inputs(r):
     if 'q' in r:
         return r['q'], r['k'], r['v'], r['do']
-    # BASELINE config 0: regenerate from the seed in the order the fixture script drew them
+    # benchmark configuration 0: regenerate from the seed in the order the fixture script drew them
     torch.manual_seed(r['seed'])
     q = torch.randn(1, 4, 4096, 64)
     k = torch.randn(1, 4, 4096, 64)
