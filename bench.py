@@ -42,21 +42,23 @@ def parse():
     return ap.parse_args()
 
 
-def clustered_inputs(heads, n, d, seed, device='cpu', dtype=torch.bfloat16):
-    """benchmark configurations 1/2: per head 64 unit-norm centroids shared by Q and K, per-token Gaussian noise of total norm
-    ~0.3, V ~ N(0,1), dO ~ N(0,1).  Seeded, generated on the CPU generator so that every rank/impl sees the same data."""
-    g = torch.Generator().manual_seed(seed)
-    cent = torch.randn(heads, 64, d, generator=g)
-    cent = cent / cent.norm(dim=-1, keepdim=True)
-    def draw():
-        a = torch.randint(0, 64, (heads, n), generator=g)
-        x = torch.gather(cent, 1, a.unsqueeze(-1).expand(-1, -1, d))
-        return x + torch.randn(heads, n, d, generator=g) * (0.3 / math.sqrt(d))
-    q = draw().unsqueeze(0)
-    k = draw().unsqueeze(0)
-    v = torch.randn(1, heads, n, d, generator=g)
-    do = torch.randn(1, heads, n, d, generator=g)
-    return [t.to(dtype).to(device) for t in (q, k, v, do)]
+def clustered_inputs(heads, n, d, seed, device='cpu', dtype=torch.bfloat16, first_head=0):
+    """Benchmark configurations 1/2: per head 64 unit-norm centroids shared by Q and K, per-token Gaussian noise of total
+    norm ~0.3, V ~ N(0,1), dO ~ N(0,1).  Every head has its own generator (seed, head index), so a rank that owns heads
+    [first_head, first_head + heads) produces exactly the slice a single process would."""
+    outs = [[], [], [], []]
+    for h in range(first_head, first_head + heads):
+        g = torch.Generator().manual_seed(seed * 100003 + h)
+        cent = torch.randn(64, d, generator=g)
+        cent = cent / cent.norm(dim=-1, keepdim=True)
+        def draw():
+            a = torch.randint(0, 64, (n,), generator=g)
+            return cent[a] + torch.randn(n, d, generator=g) * (0.3 / math.sqrt(d))
+        outs[0].append(draw().to(dtype))
+        outs[1].append(draw().to(dtype))
+        outs[2].append(torch.randn(n, d, generator=g).to(dtype))
+        outs[3].append(torch.randn(n, d, generator=g).to(dtype))
+    return [torch.stack(o).unsqueeze(0).to(device) for o in outs]
 
 
 class ClockSampler:
@@ -204,10 +206,11 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    # same data on every world size: generate all heads on the host, keep this rank's slice
-    host = clustered_inputs(heads, n, d, seed)
-    from hyperattention_b200.partition import shard_heads
-    host = [shard_heads(t, rank, world).contiguous().pin_memory() for t in host]
+    # same data on every world size: every head has its own seed, a rank generates only the heads it owns
+    from hyperattention_b200.partition import head_slice
+    mine = head_slice(heads, rank, world)
+    assert mine.stop - mine.start == hpg
+    host = [t.contiguous().pin_memory() for t in clustered_inputs(hpg, n, d, seed, first_head=mine.start)]
     q, k, v, do = [t.to(dev) for t in host]
     q, k, v = [t.requires_grad_() for t in (q, k, v)]
     gen = torch.Generator().manual_seed(1234)

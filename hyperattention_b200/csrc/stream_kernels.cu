@@ -148,7 +148,7 @@ __device__ __forceinline__ uint32_t spread4(uint32_t x) {   // bit i -> bit 2i, 
 
 // CH = d / 32 column chunks; NSET = 1 (r <= 8) or 2 (r <= 16)
 template <typename T, int CH, int NSET, int UNROLL>
-__global__ void __launch_bounds__(256) lsh_hash_mma_kernel(const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int n,
+__global__ void __launch_bounds__(256, 4) lsh_hash_mma_kernel(const T* __restrict__ x, int64_t sb, int64_t sh, int64_t sn, int H, int n,
                                                            const float* __restrict__ proj, int r, int32_t* __restrict__ codes,
                                                            long long total_rows) {
   const int lane = threadIdx.x & 31;
@@ -219,10 +219,10 @@ __global__ void __launch_bounds__(256) lsh_hash_mma_kernel(const T* __restrict__
 template <typename T, int CH>
 static void launch_hash_mma(const T* x, int64_t sb, int64_t sh, int64_t sn, int H, int n, const float* proj, int r, int32_t* codes,
                             long long total, cudaStream_t st) {
-  constexpr int UNROLL = CH <= 2 ? 4 : 2;
+  constexpr int UNROLL = CH <= 2 ? 2 : 1;   // 64 registers -> four CTAs (32 warps) per SM, each with its loads in flight
   const long long rows_per_cta = 8LL * 16 * UNROLL;
   long long want = (total + rows_per_cta - 1) / rows_per_cta;
-  const int grid = (int)(want < 148LL * 8 ? want : 148LL * 8);
+  const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
   if (r <= 8)
     lsh_hash_mma_kernel<T, CH, 1, UNROLL><<<grid, 256, 0, st>>>(x, sb, sh, sn, H, n, proj, r, codes, total);
   else
@@ -310,13 +310,27 @@ static int launch_hash(const void* x, int64_t sb, int64_t sh, int64_t sn, int B,
 __global__ void __launch_bounds__(256) gather_rows_vec_kernel(const uint8_t* __restrict__ src, int64_t sb_bytes, int64_t sh_bytes,
                                                               int64_t sn_bytes, int H, int chunks_per_row, const int32_t* __restrict__ idx,
                                                               int n_idx, uint8_t* __restrict__ dst, long long total_chunks) {
-  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total_chunks; t += (long long)gridDim.x * blockDim.x) {
-    long long orow = t / chunks_per_row;
-    int c = (int)(t - orow * chunks_per_row);
-    long long bh = orow / n_idx;
-    int srow = idx[orow];
-    const uint4* p = reinterpret_cast<const uint4*>(src + (bh / H) * sb_bytes + (bh % H) * sh_bytes + (long long)srow * sn_bytes) + c;
-    reinterpret_cast<uint4*>(dst)[t] = __ldg(p);
+  constexpr int UN = 4;   // independent copies in flight per thread
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; t0 < total_chunks; t0 += stride * UN) {
+    uint4 v[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const long long t = t0 + u * stride;
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (t < total_chunks) {
+        const long long orow = t / chunks_per_row;
+        const int c = (int)(t - orow * chunks_per_row);
+        const long long bh = orow / n_idx;
+        const int srow = __ldg(idx + orow);
+        v[u] = __ldg(reinterpret_cast<const uint4*>(src + (bh / H) * sb_bytes + (bh % H) * sh_bytes + (long long)srow * sn_bytes) + c);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const long long t = t0 + u * stride;
+      if (t < total_chunks) reinterpret_cast<uint4*>(dst)[t] = v[u];
+    }
   }
 }
 template <typename T>
