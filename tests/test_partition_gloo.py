@@ -64,3 +64,43 @@ def test_sharded_equals_unsharded_on_two_gloo_ranks(causal):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert same_o and same_lse and shape == (1, 3, 512, 32)
+
+
+def _seq_worker(rank, world, port, out_q):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        from hyperattention_b200.partition import all_gather_sequence, head_to_seq_shards, seq_to_head_shards
+        torch.manual_seed(0)
+        B, H, n, d = 2, 4, 64, 8
+        x = torch.randn(B, H, n, d)
+        m = n // world
+        x_local = x[:, :, rank * m:(rank + 1) * m].contiguous()                # sequence shard, all heads
+        xh = seq_to_head_shards(x_local)                                       # head shard, whole sequence
+        hl = H // world
+        ok1 = torch.equal(xh, x[:, rank * hl:(rank + 1) * hl])
+        back = head_to_seq_shards(xh)
+        ok2 = torch.equal(back, x_local)
+        ok3 = torch.equal(all_gather_sequence(x_local), x)
+        res = torch.tensor([int(ok1), int(ok2), int(ok3)])
+        dist.all_reduce(res, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            out_q.put(res.tolist())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_shard_ingress_on_two_gloo_ranks():
+    ctx = mp.get_context('spawn')
+    out_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_seq_worker, args=(r, 2, port, out_q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = out_q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res == [1, 1, 1]
