@@ -36,6 +36,7 @@ class AttnParams(C.Structure):
         ('d_o', vp), ('do_sb', i64), ('do_sh', i64), ('do_sn', i64),
         ('delta', vp), ('dq_acc', vp), ('dk_acc', vp), ('dv_acc', vp),
         ('status', vp),
+        ('sample_logw', vp), ('sample_mask', vp),
     ]
 
 
@@ -63,6 +64,7 @@ SIGNATURES = {
     'ha_gather_rows': (C.c_int, [vp, i64, i64, i64, i32, i32, i32, i32, vp, i32, vp, vp]),
     'ha_attn_fwd': (C.c_int, [C.POINTER(AttnParams), vp]),
     'ha_attn_bwd': (C.c_int, [C.POINTER(AttnParams), vp]),
+    'ha_sample_weights': (C.c_int, [vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     'ha_delta': (C.c_int, [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, i32, vp, vp]),
     'ha_cast_from_f32': (C.c_int, [vp, vp, i64, i32, vp]),
     'ha_lse_merge': (C.c_int, [vp, vp, vp, vp, i64, i32, i32, i32, vp]),

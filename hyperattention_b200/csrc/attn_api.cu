@@ -25,6 +25,7 @@ static int check_common(const ha_attn_params& p, bool backward) {
     if (p.sample_size > p.m_k) return HA_ERR_INVALID;   // the reference would read past the head here
     if (!p.q_idx || !p.k_idx) return HA_ERR_INVALID;
     if (p.flags & HA_FLAG_CAUSAL) return HA_ERR_INVALID;
+    if ((p.sample_logw == nullptr) != (p.sample_mask == nullptr)) return HA_ERR_INVALID;
   } else if (p.mode == HA_MODE_FLASH) {
     if ((p.flags & HA_FLAG_CAUSAL) && p.m_q != p.m_k) return HA_ERR_INVALID;
     if (p.m_q > 0 && p.m_k == 0) return HA_ERR_INVALID;

@@ -46,6 +46,12 @@ __device__ __forceinline__ int fwd_key_row(const ha_attn_params& p, int seg, con
   return p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + s] : s;
 }
 
+// weighted sampling: is slot s dropped for sorted query tile t of this segment?
+__device__ __forceinline__ bool slot_dropped(const ha_attn_params& p, int seg, int t, int s) {
+  const long long base = ((long long)seg * (p.m_q / TILE) + t) * (p.sample_size / 32);
+  return (p.sample_mask[base + (s >> 5)] >> (s & 31)) & 1u;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_fwd_kernel(const ha_attn_params p, long long total_queries) {
   __shared__ float sq[SIMT_WARPS][MAXD];
@@ -65,11 +71,14 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_fwd_kernel(const ha
 
   Window w{0, 0};
   int n_blk = 0, n_keys;
+  const bool weighted = hyper && p.sample_logw != nullptr;
+  float logw = 0.f;
   if (hyper) {
     const int bs = (p.block_size + TILE - 1) / TILE;
     w = block_window(pos / TILE, bs, p.m_k, p.flags & HA_FLAG_SMOOTH);
     n_blk = w.count;
     n_keys = n_blk + p.sample_size;
+    if (weighted) logw = p.sample_logw[(long long)seg * (p.m_q / TILE) + pos / TILE];
   } else {
     n_keys = (p.flags & HA_FLAG_CAUSAL) ? min(pos + 1, p.m_k) : p.m_k;
   }
@@ -80,9 +89,11 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_fwd_kernel(const ha
   for (int i = 0; i < VR; ++i) acc[i] = 0.f;
   float mx = -INFINITY, l = 0.f;
   for (int j0 = 0; j0 < n_keys; j0 += 32) {
-    const int krow = fwd_key_row(p, seg, w, n_blk, j0 + lane, n_keys);
+    int krow = fwd_key_row(p, seg, w, n_blk, j0 + lane, n_keys);
+    const bool sampled = weighted && j0 + lane >= n_blk && krow >= 0;
+    if (sampled && slot_dropped(p, seg, pos / TILE, j0 + lane - n_blk)) krow = -1;
     float s = -INFINITY;
-    if (krow >= 0) s = dot_row<T>(sq[warp], kbase + (long long)krow * p.k_sn, p.d) * p.scale;
+    if (krow >= 0) s = dot_row<T>(sq[warp], kbase + (long long)krow * p.k_sn, p.d) * p.scale + (sampled ? logw : 0.f);
     float gm = s;
     for (int off = 16; off >= 1; off >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, off));
     const float mnew = fmaxf(mx, gm);
@@ -98,6 +109,7 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_fwd_kernel(const ha
     for (int jj = 0; jj < cnt; ++jj) {
       const float pb = __shfl_sync(0xffffffffu, pj, jj);
       const int rb = __shfl_sync(0xffffffffu, krow, jj);
+      if (rb < 0) continue;
       const T* vp = vbase + (long long)rb * p.v_sn;
 #pragma unroll
       for (int i = 0; i < VR; ++i) {
@@ -201,7 +213,7 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_bwd_kernel(const ha
     ql = {p.m_q - first, 1, first, 0, 0};
   } else if (phase == 1) {
     krow = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + kk] : kk;
-    ql = {p.m_q, 1, 0, 0, 0};
+    ql = {p.m_q, p.sample_logw ? 0 : 1, 0, 0, 0};   // weighted: by sorted position, so that j / 128 is the query tile
   } else {
     krow = p.k_idx[(long long)seg * p.m_k + kk];
     const int t = kk / TILE;
@@ -238,9 +250,14 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_bwd_kernel(const ha
     const int j = j0 + lane;
     int qrow = -1;
     if (j < j_end) qrow = qlist_row(p, seg, ql, j, kk, bs);
+    float logw = 0.f;
+    if (hyper && phase == 1 && p.sample_logw && qrow >= 0) {
+      if (slot_dropped(p, seg, j / TILE, kk)) qrow = -1;
+      else logw = p.sample_logw[(long long)seg * (p.m_q / TILE) + j / TILE];
+    }
     float pj = 0.f, ds = 0.f;
     if (qrow >= 0) {
-      const float s = dot_row<T>(sk[warp], qbase + (long long)qrow * p.q_sn, p.d) * p.scale;
+      const float s = dot_row<T>(sk[warp], qbase + (long long)qrow * p.q_sn, p.d) * p.scale + logw;
       const float dp = dot_row<T>(sv[warp], gbase + (long long)qrow * p.do_sn, p.dv);
       pj = expf(s - p.lse[stat0 + qrow]);
       ds = pj * (dp - p.delta[stat0 + qrow]) * p.scale;

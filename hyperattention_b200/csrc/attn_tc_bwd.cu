@@ -156,6 +156,11 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
     it.qt_first = z * BWD_CHUNK;
     if (!hyper && (p.flags & HA_FLAG_CAUSAL)) it.qt_first = max(it.qt_first, it.k_tile);
     it.qt_count = min((z + 1) * BWD_CHUNK, n_qt) - it.qt_first;
+    if (hyper && p.sample_logw) {
+      // weighted sampling: the weight and the dropped slots belong to SORTED query tiles, so walk those
+      it.q_sorted = true;
+      it.q_pos0 = it.qt_first * TILE;
+    }
   }
   return it;
 }
@@ -306,9 +311,22 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     }
   };
   // P and dS of this thread's query row, its group's 64 key columns -> shared memory
-  auto elementwise = [&](float lse2, float dlt, bool masked) {
-    const int limit = masked ? row + 1 : TILE;
-    const uint64_t sc2 = pack_f2(scale2, scale2), nlse = pack_f2(-lse2, -lse2);
+  // weighted sampling (sampled items only): pair jj meets sorted query tile qt_first + jj; its log weight is added to
+  // the scores and the dropped slots among this group's 64 key columns give p = 0
+  const bool weighted = hyper && p.sample_logw && item >= items_blk;
+  auto elementwise = [&](float lse2, float dlt, bool diag, int jj) {
+    const int limit = diag ? row + 1 : TILE;
+    uint32_t wm[2] = {0u, 0u};
+    float bias2 = 0.f;
+    if (weighted) {
+      const long long qtile = (long long)seg * (p.m_q / TILE) + qt_first + jj;
+      const uint32_t* mw = p.sample_mask + qtile * (p.sample_size / 32) + k_tile * 4 + wg * 2;
+      wm[0] = mw[0];
+      wm[1] = mw[1];
+      bias2 = p.sample_logw[qtile] * LOG2E;
+    }
+    const bool masked = diag || (wm[0] | wm[1]) != 0u;
+    const uint64_t sc2 = pack_f2(scale2, scale2), nlse = pack_f2(bias2 - lse2, bias2 - lse2);
     const uint64_t scl = pack_f2(p.scale, p.scale), ndel = pack_f2(-dlt * p.scale, -dlt * p.scale);
     const int col0 = wg * 64;
 #pragma unroll
@@ -328,8 +346,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
           p0 = fast_exp2(p0);
           p1 = fast_exp2(p1);
           if (masked) {
-            if (col0 + c * 32 + i + e >= limit) p0 = 0.f;
-            if (col0 + c * 32 + i + e + 1 >= limit) p1 = 0.f;
+            if (col0 + c * 32 + i + e >= limit || ((wm[c] >> (i + e)) & 1u)) p0 = 0.f;
+            if (col0 + c * 32 + i + e + 1 >= limit || ((wm[c] >> (i + e + 1)) & 1u)) p1 = 0.f;
           }
           // ds = p * (dp - delta) * scale
           unpack_f2(fmul2(pack_f2(p0, p1), ffma2(pack_u2(rp[i + e], rp[i + e + 1]), scl, ndel)), d0, d1);
@@ -406,7 +424,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
         qrow_after = q_row(jj + 2);
       }
       HA_T_MARK(2)
-      elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile);
+      elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile, jj);
       HA_T_MARK(3)
       cp_async_wait<0>();                     // query tile jj+1 has landed
       fence_async_smem();
@@ -468,7 +486,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       tc_fence_after();
       if (__syncthreads_or(failed)) { failed = true; break; }
       HA_T_MARK(2)
-      elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile);
+      elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile, jj);
       fence_async_smem();
       tc_fence_before();
       __syncthreads();

@@ -269,6 +269,16 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
     // visible columns of this row: all of them, except on a causal diagonal tile or a ragged last tile
     int limit = TILE;
     bool masked = false;   // uniform over the CTA
+    // weighted sampling: a sampled tile's scores get the tile's log weight, and its dropped slots are masked
+    uint32_t wm[4] = {0u, 0u, 0u, 0u};
+    float bias2 = 0.f;
+    if (hyper && p.sample_logw && j >= tl.n_blk) {
+      const long long qtile = (long long)seg * n_qt + qt;
+      const uint32_t* mw = p.sample_mask + qtile * (p.sample_size / 32) + (j - tl.n_blk) * 4;
+      wm[0] = mw[0]; wm[1] = mw[1]; wm[2] = mw[2]; wm[3] = mw[3];
+      bias2 = p.sample_logw[qtile] * 1.4426950408889634f;
+      masked = (wm[0] | wm[1] | wm[2] | wm[3]) != 0u;
+    }
     if (!hyper) {
       limit = min(TILE, p.m_k - j * TILE);
       masked = limit < TILE;
@@ -299,18 +309,18 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < limit) m0 = fmaxf(m0, __uint_as_float(cur[i]));
+            if (c * 32 + i < limit && !((wm[c] >> i) & 1u)) m0 = fmaxf(m0, __uint_as_float(cur[i]));
         }
         if (c + 1 < 4) tmem_ld_fence(nxt);
       }
       mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
     }
-    const float m_new = fmaxf(m_run, mx * scale2);
+    const float m_new = fmaxf(m_run, mx * scale2 + bias2);
     const float m_use = m_new == -INFINITY ? 0.f : m_new;
     const float alpha = fast_exp2(m_run - m_use);   // m_run = -inf -> 0
     float psum;
     {
-      const uint64_t sc2 = pack_f2(scale2, scale2), negm = pack_f2(-m_use, -m_use);
+      const uint64_t sc2 = pack_f2(scale2, scale2), negm = pack_f2(bias2 - m_use, bias2 - m_use);
       uint64_t ps_a = pack_f2(0.f, 0.f), ps_b = ps_a;
       uint32_t ra[32], rb[32];
       tmem_ld32(tS + lane_sel, ra);
@@ -330,10 +340,10 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
           unpack_f2(ffma2(pack_u2(cur[i + 2], cur[i + 3]), sc2, negm), p2, p3);
           p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
           if (masked) {
-            if (c * 32 + i >= limit) p0 = 0.f;
-            if (c * 32 + i + 1 >= limit) p1 = 0.f;
-            if (c * 32 + i + 2 >= limit) p2 = 0.f;
-            if (c * 32 + i + 3 >= limit) p3 = 0.f;
+            if (c * 32 + i >= limit || ((wm[c] >> i) & 1u)) p0 = 0.f;
+            if (c * 32 + i + 1 >= limit || ((wm[c] >> (i + 1)) & 1u)) p1 = 0.f;
+            if (c * 32 + i + 2 >= limit || ((wm[c] >> (i + 2)) & 1u)) p2 = 0.f;
+            if (c * 32 + i + 3 >= limit || ((wm[c] >> (i + 3)) & 1u)) p3 = 0.f;
           }
           ps_a = fadd2(ps_a, pack_f2(p0, p1));
           ps_b = fadd2(ps_b, pack_f2(p2, p3));

@@ -1,5 +1,6 @@
 // HBM-bound streaming kernels: angular LSH hash, row gather, delta (rowwise o.do), fp32->dtype cast, LSE merge.
 #include "common.cuh"
+#include "attn_index.cuh"
 
 #include <mutex>
 #include <string>
@@ -474,6 +475,38 @@ static inline int grid_for(long long items, int per_cta) {
 
 using namespace ha;
 
+
+// ---------------------------------------------------------------------------------------------------
+// Weights of uniformly sampled key columns: inverse key permutation, then per query tile the dropped slots
+// (keys already inside the tile's block window) and the log importance weight of the kept ones.
+// ---------------------------------------------------------------------------------------------------
+__global__ void invert_perm_kernel(const int32_t* __restrict__ idx, int32_t* __restrict__ inv, int m, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long seg = i / m;
+  inv[seg * m + idx[i]] = (int32_t)(i - seg * m);
+}
+
+__global__ void __launch_bounds__(128) sample_weights_kernel(const int32_t* __restrict__ inv, const int32_t* __restrict__ sample_idx,
+                                                             int m, int bs, int S, int smooth, float* __restrict__ tile_logw,
+                                                             uint32_t* __restrict__ tile_mask) {
+  const int t = blockIdx.x, T_ = gridDim.x;
+  const long long seg = blockIdx.y;
+  const ha::Window w = ha::block_window(t, bs, m, smooth != 0);
+  int kept = 0;
+  for (int s0 = 0; s0 < S; s0 += 128) {           // S is a multiple of 128: every thread makes every trip
+    const int s = s0 + threadIdx.x;
+    const int row = sample_idx ? sample_idx[seg * S + s] : s;
+    int off = inv[seg * m + row] - w.first;
+    if (off < 0) off += m;
+    const bool dropped = off < w.count;
+    const unsigned bits = __ballot_sync(0xffffffffu, dropped);
+    if ((threadIdx.x & 31) == 0) tile_mask[(seg * T_ + t) * (S / 32) + (s >> 5)] = bits;
+    kept += __syncthreads_count(!dropped);
+  }
+  if (threadIdx.x == 0) tile_logw[seg * T_ + t] = kept > 0 ? logf((float)(m - w.count) / (float)kept) : -INFINITY;
+}
+
 extern "C" {
 
 const char* ha_version(void) { return "hyperattn_b200 0.1 (sm_100a)"; }
@@ -583,6 +616,25 @@ int ha_lse_merge(void* o1, float* lse1, const void* o2, const float* lse2, int64
     default: return HA_ERR_DTYPE;
   }
   HA_LAUNCHED("ha_lse_merge");
+  return HA_OK;
+}
+
+int ha_sample_weights(const int32_t* k_idx, const int32_t* sample_idx, int32_t segs, int32_t m, int32_t block_size,
+                      int32_t sample_size, int32_t smooth, int32_t* inv_workspace, float* tile_logw, uint32_t* tile_mask,
+                      void* stream) {
+  if (segs < 0 || m < 0 || block_size <= 0 || sample_size < 0) return HA_ERR_INVALID;
+  if (m % TILE || sample_size % TILE || sample_size > m) return HA_ERR_INVALID;
+  if (segs == 0 || m == 0 || sample_size == 0) return HA_OK;
+  if (!k_idx || !inv_workspace || !tile_logw || !tile_mask) return HA_ERR_INVALID;
+  if (segs > 65535) return HA_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long total = (long long)segs * m;
+  if ((total + 255) / 256 > 0x7fffffffLL) return HA_ERR_TOO_LARGE;
+  invert_perm_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(k_idx, inv_workspace, m, total);
+  HA_LAUNCHED("ha_sample_weights (invert)");
+  sample_weights_kernel<<<dim3(m / TILE, segs), 128, 0, st>>>(inv_workspace, sample_idx, m, (block_size + TILE - 1) / TILE,
+                                                             sample_size, smooth, tile_logw, tile_mask);
+  HA_LAUNCHED("ha_sample_weights");
   return HA_OK;
 }
 

@@ -77,7 +77,14 @@ class HyperAttention(torch.nn.Module):
         self.merge_mode = kwargs.get('merge_mode', 'reference')
         self.fused_causal = kwargs.get('fused_causal', True)
         self.kernel_flags = kwargs.get('kernel_flags', 0)
+        # 'reference': sampled part = key rows 0..sample_size-1, unweighted (what the reference's kernels compute).
+        # 'uniform':   sample_size distinct key rows drawn uniformly per (batch, head), the query tile's own block
+        #              excluded, importance-weighted to stand for all keys outside the block (no reference counterpart).
+        self.sampling = kwargs.get('sampling', 'reference')
+        self.sample_generator = kwargs.get('sample_generator')   # torch.Generator on the inputs' device, or None
+        self.last_sample_idx = None
         assert self.grad_mode in ('reference', 'exact') and self.merge_mode in ('reference', 'exact')
+        assert self.sampling in ('reference', 'uniform')
         self.lsh = AngularLSH(num_projs=self.lsh_num_projs, dim=(1, 1, input_dim), rng=kwargs.get('rng'))
 
     # ------------------------------------------------------------------------------------------
@@ -123,7 +130,7 @@ class HyperAttention(torch.nn.Module):
             attn, lse = ops.flash_attn_func(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), None, True,
                                             scale, self.kernel_flags & L.FLAG_FORCE_SIMT)
             attn = attn.transpose(1, 2)
-        elif self.fused_causal and self._regular_causal(n_key):
+        elif self.fused_causal and self.sampling == 'reference' and self._regular_causal(n_key):
             attn, lse = ops.CausalHyperFunc.apply(query, key, value, self.lsh.proj_f32(), self._causal_levels(n_key),
                                                   self.block_size, self.sample_size, scale, self._flags(),
                                                   self.grad_mode == 'reference')
@@ -171,8 +178,15 @@ class HyperAttention(torch.nn.Module):
             bits = self.lsh_num_projs
             q_idx = ops.seg_sort(self.lsh.hash_cuda(query), bits).view(B, H, n_query)
             k_idx = ops.seg_sort(self.lsh.hash_cuda(key), bits).view(B, H, key.shape[2])
+            sample_idx, weighted = None, False
+            if self.sampling == 'uniform' and self.sample_size > 0:
+                # distinct uniform rows per (batch, head): the positions of the largest of n uniform variates
+                u = torch.rand(B * H, key.shape[2], device=key.device, generator=self.sample_generator)
+                sample_idx = u.topk(self.sample_size, dim=-1).indices.to(torch.int32)
+                self.last_sample_idx = sample_idx.view(B, H, self.sample_size)
+                weighted = True
             attn, lse = ops.hyper_attn_func(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2),
                                             q_idx.transpose(1, 2), k_idx.transpose(1, 2), self.block_size, self.sample_size,
-                                            scale, self.smooth_block, None, self._flags() & ~L.FLAG_SMOOTH)
+                                            scale, self.smooth_block, sample_idx, self._flags() & ~L.FLAG_SMOOTH, weighted)
         attn = attn.transpose(1, 2)
         return attn, lse.unsqueeze(-1)

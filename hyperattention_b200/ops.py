@@ -152,13 +152,29 @@ def _idx_rows(idx, B, n, H):
     return idx.transpose(1, 2).to(torch.int32).contiguous().view(B * H, n)
 
 
+def sample_weights(k_idx_rows, sample_rows, n, block_size, sample_size, smooth_block):
+    """Per sorted query tile: log importance weight of the kept sampled slots and the bit mask of the dropped ones
+    (ha_sample_weights).  k_idx_rows int32 [segs, n]; sample_rows int32 [segs, sample_size] or None (rows 0..S-1).
+    Returns (logw float32 [segs, n/128], mask int32 [segs, n/128, sample_size/32])."""
+    segs = k_idx_rows.shape[0]
+    dev = k_idx_rows.device
+    inv = torch.empty(segs, n, dtype=torch.int32, device=dev)
+    logw = torch.empty(segs, n // 128, dtype=torch.float32, device=dev)
+    mask = torch.empty(segs, n // 128, sample_size // 32, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = L.load().ha_sample_weights(_ptr(k_idx_rows), _ptr(sample_rows), segs, n, block_size, sample_size,
+                                        1 if smooth_block else 0, _ptr(inv), _ptr(logw), _ptr(mask), _stream())
+    L.check(rc, 'ha_sample_weights')
+    return logw, mask
+
+
 class HyperAttnFunc(torch.autograd.Function):
     """Drop-in for HyperAttnFunc (src/hyper_attn_triton.py:895-945): q, k, v [B, n, H, d] views, permutations
     [B, n, H]; returns o [B, n, H, dv] and lse [B, H, n]; the gradient flowing into lse is discarded, as there."""
 
     @staticmethod
     def forward(ctx, q, k, v, q_sort_idx, k_sort_idx, block_size, sample_size=0, softmax_scale=None, smooth_block=False,
-                sample_idx=None, flags=0):
+                sample_idx=None, flags=0, weighted=False):
         _cuda(q, k, v, q_sort_idx, k_sort_idx)
         q, k, v = [x if x.stride(-1) == 1 else x.contiguous() for x in (q, k, v)]
         assert sample_size % 128 == 0
@@ -189,17 +205,24 @@ class HyperAttnFunc(torch.autograd.Function):
         p.o_sb, p.o_sh, p.o_sn = _bhn(o)
         p.lse = _ptr(lse)
         p.status = _ptr(_status_word(q.device))
+        wts = None
+        if weighted and sample_size > 0:
+            # importance-weighted sampled columns, the query tile's own block excluded (not in the reference's code)
+            wts = sample_weights(ki, si, n, block_size, sample_size, smooth_block)
+            p.sample_logw, p.sample_mask = _ptr(wts[0]), _ptr(wts[1])
         with torch.cuda.device(q.device):
             rc = L.load().ha_attn_fwd(C.byref(p), _stream())
         L.check(rc, 'ha_attn_fwd')
-        ctx.save_for_backward(q, k, v, qi, ki, o, lse, si if si is not None else torch.empty(0, device=q.device))
-        ctx.cfg = (block_size, sample_size, scale, p.flags, si is not None)
+        empty = torch.empty(0, device=q.device)
+        ctx.save_for_backward(q, k, v, qi, ki, o, lse, si if si is not None else empty,
+                              *(wts if wts is not None else (empty, empty)))
+        ctx.cfg = (block_size, sample_size, scale, p.flags, si is not None, wts is not None)
         return o, lse
 
     @staticmethod
     def backward(ctx, do, dlse_unused=None):
-        q, k, v, qi, ki, o, lse, si = ctx.saved_tensors
-        block_size, sample_size, scale, flags, has_si = ctx.cfg
+        q, k, v, qi, ki, o, lse, si, logw, mask = ctx.saved_tensors
+        block_size, sample_size, scale, flags, has_si, has_w = ctx.cfg
         if do.stride(-1) != 1:
             do = do.contiguous()
         B, n, H, d = q.shape
@@ -211,12 +234,13 @@ class HyperAttnFunc(torch.autograd.Function):
         with torch.cuda.device(dev):
             rc = lib.ha_delta(_ptr(o), *_bhn(o), _ptr(do), *_bhn(do), B, H, n, dv, _dtype_id(q), _ptr(delta), _stream())
             L.check(rc, 'ha_delta')
-            hyper_bwd_launch(q, k, v, qi, ki, si if has_si else None, o, lse, do, delta, acc, block_size, sample_size, scale, flags)
+            hyper_bwd_launch(q, k, v, qi, ki, si if has_si else None, o, lse, do, delta, acc, block_size, sample_size, scale, flags,
+                             (logw, mask) if has_w else None)
             grads = _cast_grads(lib, acc, q.dtype, B, H, n, d, dv)
-        return grads + (None,) * 8
+        return grads + (None,) * 9
 
 
-def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sample_size, scale, flags):
+def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sample_size, scale, flags, weights=None):
     """One ha_attn_bwd call (HA_MODE_HYPER) on [B, n, H, *] views; acc = zeroed fp32 buffer holding dq | dk | dv
     accumulators ([B,H,n,d], [B,H,n,d], [B,H,n,dv] back to back).  Nothing else is launched."""
     B, n, H, d = q.shape
@@ -237,6 +261,8 @@ def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sa
     p.delta = _ptr(delta)
     p.dq_acc, p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr()), C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
     p.status = _ptr(_status_word(q.device))
+    if weights is not None:
+        p.sample_logw, p.sample_mask = _ptr(weights[0]), _ptr(weights[1])
     rc = L.load().ha_attn_bwd(C.byref(p), _stream())
     L.check(rc, 'ha_attn_bwd')
 
@@ -257,9 +283,9 @@ def _cast_grads(lib, acc, dtype, B, H, n, d, dv):
 
 
 def hyper_attn_func(q, k, v, q_sort_idx, k_sort_idx, block_size, sample_size=0, softmax_scale=None, smooth_block=False,
-                    sample_idx=None, flags=0):
+                    sample_idx=None, flags=0, weighted=False):
     return HyperAttnFunc.apply(q, k, v, q_sort_idx, k_sort_idx, block_size, sample_size, softmax_scale, smooth_block,
-                               sample_idx, flags)
+                               sample_idx, flags, weighted)
 
 
 class FlashAttnFunc(torch.autograd.Function):

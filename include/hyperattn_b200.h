@@ -109,6 +109,9 @@ int ha_gather_rows(const void* src, int64_t stride_b, int64_t stride_h, int64_t 
  * the backward, _bwd_preprocess_do_o_dot, _bwd_permuted_block_diagonal_kernel and _bwd_sampled_col_kernel
  * (:196-236, :399-506, :517-665).  q_idx / k_idx: int32 [B*H*segs_per_head][m] local sorted positions -> local row;
  * sample_idx: int32 [B*H*segs_per_head][sample_size] local key rows (NULL = 0..sample_size-1, the reference's choice).
+ * sample_logw / sample_mask (both or neither; outputs of ha_sample_weights): the sampled rows become an importance-
+ * weighted estimate of the keys outside each query tile's block window.  No counterpart in the reference's code,
+ * whose sampled part always reads rows 0..sample_size-1 unweighted (src/hyper_attn_triton.py:139-176).
  * HA_MODE_FLASH replaces flash_attn_func / _fwd_kernel / _bwd_kernel (src/flash_attn_triton.py:995-1042, :57-267,
  * :651-792) without the bias branch.
  *
@@ -138,10 +141,22 @@ typedef struct {
   const float* delta;              /* [B,H,n]: sum_d o*do of the part this call differentiates */
   float *dq_acc, *dk_acc, *dv_acc; /* fp32 [B,H,n,d], [B,H,n,d], [B,H,n,dv] contiguous accumulators (added into) */
   int32_t* status;                 /* optional device status word (0 = ok) */
+  const float* sample_logw;        /* optional [B*H*segs_per_head][m_q/128]: log weight of the kept sampled slots */
+  const uint32_t* sample_mask;     /* optional [B*H*segs_per_head][m_q/128][sample_size/32]: bit s = slot s dropped */
 } ha_attn_params;
 
 int ha_attn_fwd(const ha_attn_params* p, void* stream);
 int ha_attn_bwd(const ha_attn_params* p, void* stream);
+
+/* Weights of uniformly sampled key columns (no counterpart in the reference's code; its paper's estimator).
+ * For every sorted query tile t of every segment: slot s of sample_idx is dropped (mask bit set) when that key's
+ * sorted position lies inside the tile's block window, and tile_logw = log((m - window size) / kept slots), so that
+ * the kept samples stand for all keys outside the window (-inf when none is kept).  m = rows per segment (a
+ * multiple of 128), sample_size a multiple of 128; sample_idx entries must be distinct rows in [0, m).
+ * inv_workspace: int32 [segs][m] scratch.  tile_logw: [segs][m/128].  tile_mask: [segs][m/128][sample_size/32]. */
+int ha_sample_weights(const int32_t* k_idx, const int32_t* sample_idx, int32_t segs, int32_t m, int32_t block_size,
+                      int32_t sample_size, int32_t smooth, int32_t* inv_workspace, float* tile_logw,
+                      uint32_t* tile_mask, void* stream);
 
 /* delta[b,h,i] = sum_e o[b,h,i,e] * do[b,h,i,e].  Replaces _bwd_preprocess_do_o_dot (src/hyper_attn_triton.py:196-236,
  * src/flash_attn_triton.py:271-312). */

@@ -107,11 +107,29 @@ def _default_sample_idx(sample_size: int, device=None) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 # Fused block-diagonal + sampled attention, one (batch, head) at a time
 # --------------------------------------------------------------------------------------------
-def _hyper_fwd_head(q, k, v, qi, ki, block_size, sample_idx, scale, smooth):
+def sample_tile_weights(n, ki, block_size, sample_idx, smooth):
+    """Weighted sampling (no counterpart in the mounted reference; "parity unpinned"): for every sorted query tile t,
+    which sampled slots are dropped because their key already lies in the tile's block window, and the log of the
+    importance weight (n - window size) / (number of kept slots) that makes the kept samples stand for all keys
+    outside the window.  Returns (masked [T, S] bool, logw [T] float; -inf where nothing is kept)."""
+    pos, valid = block_window_positions(n, block_size, smooth)
+    inv = torch.empty(n, dtype=torch.int64)
+    inv[ki] = torch.arange(n)
+    spos = inv[sample_idx]                                           # sorted position of every sampled key
+    count = valid.sum(-1)                                            # window size per tile
+    first = pos[:, 0]
+    masked = ((spos[None, :] - first[:, None]) % n) < count[:, None]
+    kept = (~masked).sum(-1)
+    logw = torch.where(kept > 0, torch.log((n - count).float() / kept.clamp_min(1).float()), torch.full((len(count),), float('-inf')))
+    return masked, logw
+
+
+def _hyper_fwd_head(q, k, v, qi, ki, block_size, sample_idx, scale, smooth, weighted=False):
     """q,k [n,d], v [n,dv] float32; qi,ki [n] int64; returns o [n,dv], lse [n] at original rows.
 
     src/hyper_attn_triton.py:70-192: for the sorted query tile t the key multiset is the block window
     (gathered through k_sort_idx) followed by the sampled rows (original order); one softmax over both.
+    weighted=True switches the sampled part to the importance-weighted estimator of sample_tile_weights.
     """
     n, d = q.shape
     n_tiles = n // TILE
@@ -126,6 +144,10 @@ def _hyper_fwd_head(q, k, v, qi, ki, block_size, sample_idx, scale, smooth):
         ksm = k[sample_idx]
         vsm = v[sample_idx]
         s_smp = torch.einsum('tmd,sd->tms', qs, ksm) * scale
+        if weighted:
+            masked, logw = sample_tile_weights(n, ki, block_size, sample_idx, smooth)
+            s_smp = (s_smp + logw[:, None, None]).masked_fill(masked[:, None, :], float('-inf'))
+            s_smp = torch.nan_to_num(s_smp, nan=float('-inf'))
         s_all = torch.cat([s_blk, s_smp], dim=-1)
     else:
         s_all = s_blk
@@ -142,7 +164,7 @@ def _hyper_fwd_head(q, k, v, qi, ki, block_size, sample_idx, scale, smooth):
     return o, lse
 
 
-def _hyper_bwd_head(q, k, v, qi, ki, do, lse, delta, block_size, sample_idx, scale, smooth, exact_pattern):
+def _hyper_bwd_head(q, k, v, qi, ki, do, lse, delta, block_size, sample_idx, scale, smooth, exact_pattern, weighted=False):
     """Gradients for one head (all float32, original row order).
 
     src/hyper_attn_triton.py:289-388 (block part, enumerated per sorted *key* tile) and :573-663
@@ -189,6 +211,12 @@ def _hyper_bwd_head(q, k, v, qi, ki, do, lse, delta, block_size, sample_idx, sca
     if sample_idx is not None and sample_idx.numel() > 0:
         ksm, vsm = k[sample_idx], v[sample_idx]
         s = (q @ ksm.t()) * scale
+        if weighted:
+            masked, logw = sample_tile_weights(n, ki, block_size, sample_idx, smooth)
+            tile_of_row = torch.empty(n, dtype=torch.int64)
+            tile_of_row[qi] = torch.arange(n) // TILE                  # sorted tile of every original row
+            s = (s + logw[tile_of_row][:, None]).masked_fill(masked[tile_of_row], float('-inf'))
+            s = torch.nan_to_num(s, nan=float('-inf'))
         p = torch.exp(s - lse[:, None])
         dp = do @ vsm.t()
         ds = p * (dp - delta[:, None]) * scale
@@ -210,7 +238,7 @@ class _HyperAttnOracleFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, q_sort_idx, k_sort_idx, block_size, sample_size, softmax_scale, smooth_block,
-                sample_idx, exact_pattern):
+                sample_idx, exact_pattern, weighted=False):
         B, n, H, d = q.shape
         assert n % TILE == 0, 'sequence length must be divisible by 128 (src/hyper_attn_triton.py:695)'
         scale = softmax_scale or 1.0 / math.sqrt(d)
@@ -226,17 +254,17 @@ class _HyperAttnOracleFn(torch.autograd.Function):
         for b in range(B):
             for h in range(H):
                 o[b, h], lse[b, h] = _hyper_fwd_head(qf[b, h], kf[b, h], vf[b, h], qi[b, h], ki[b, h], block_size,
-                                                     None if sidx is None else sidx[b, h], scale, bool(smooth_block))
+                                                     None if sidx is None else sidx[b, h], scale, bool(smooth_block), weighted)
         o_out = o.to(q.dtype).transpose(1, 2)          # [B, n, H, dv] view, like the reference's o
         ctx.save_for_backward(q, k, v, qi, ki, o_out, lse)
         ctx.sidx = sidx
-        ctx.args = (block_size, scale, bool(smooth_block), bool(exact_pattern))
+        ctx.args = (block_size, scale, bool(smooth_block), bool(exact_pattern), bool(weighted))
         return o_out, lse
 
     @staticmethod
     def backward(ctx, do, dlse_unused=None):
         q, k, v, qi, ki, o, lse = ctx.saved_tensors
-        block_size, scale, smooth, exact_pattern = ctx.args
+        block_size, scale, smooth, exact_pattern, weighted = ctx.args
         B, n, H, d = q.shape
         qf, kf, vf, dof, of = _to_bh(q), _to_bh(k), _to_bh(v), _to_bh(do), _to_bh(o)
         delta = (of * dof).sum(-1)                      # src/hyper_attn_triton.py:196-236
@@ -247,16 +275,17 @@ class _HyperAttnOracleFn(torch.autograd.Function):
             for h in range(H):
                 dq[b, h], dk[b, h], dv[b, h] = _hyper_bwd_head(
                     qf[b, h], kf[b, h], vf[b, h], qi[b, h], ki[b, h], dof[b, h], lse[b, h], delta[b, h], block_size,
-                    None if ctx.sidx is None else ctx.sidx[b, h], scale, smooth, exact_pattern)
+                    None if ctx.sidx is None else ctx.sidx[b, h], scale, smooth, exact_pattern, weighted)
         cast = lambda t, like: t.transpose(1, 2).to(like.dtype)
-        return cast(dq, q), cast(dk, k), cast(dv, v), None, None, None, None, None, None, None, None
+        return cast(dq, q), cast(dk, k), cast(dv, v), None, None, None, None, None, None, None, None, None
 
 
 def hyper_attn_func(q, k, v, q_sort_idx, k_sort_idx, block_size, sample_size=0, softmax_scale=None,
-                    smooth_block=False, sample_idx=None, exact_pattern=False):
-    """Oracle twin of hyper_attn_func (src/hyper_attn_triton.py:948)."""
+                    smooth_block=False, sample_idx=None, exact_pattern=False, weighted=False):
+    """Oracle twin of hyper_attn_func (src/hyper_attn_triton.py:948).  weighted=True (with an explicit sample_idx):
+    importance-weighted sampled columns excluding the query tile's own block (sample_tile_weights)."""
     return _HyperAttnOracleFn.apply(q, k, v, q_sort_idx, k_sort_idx, block_size, sample_size, softmax_scale,
-                                    smooth_block, sample_idx, exact_pattern)
+                                    smooth_block, sample_idx, exact_pattern, weighted)
 
 
 # --------------------------------------------------------------------------------------------

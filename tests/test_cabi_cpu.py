@@ -32,7 +32,7 @@ def test_every_declared_symbol_is_exported(lib):
 def test_struct_layout_matches_header(lib):
     """sizes computed from the header's field lists with natural alignment"""
     from hyperattention_b200 import _lib
-    assert C.sizeof(_lib.AttnParams) == 17 * 4 + 4 + 3 * 8 + 9 * 8 + 3 * 8 + 8 + 3 * 8 + 3 * 8 + 8 + 3 * 8 + 4 * 8 + 8
+    assert C.sizeof(_lib.AttnParams) == 17 * 4 + 4 + 3 * 8 + 9 * 8 + 3 * 8 + 8 + 3 * 8 + 3 * 8 + 8 + 3 * 8 + 4 * 8 + 8 + 2 * 8
     assert C.sizeof(_lib.CausalParams) == 12 * 4 + 4 + 4 + 6 * 8 + 4 * 8 + 5 * 8
 
 
@@ -55,6 +55,13 @@ def test_argument_validation_without_a_gpu(lib):
     assert lib.ha_attn_fwd(C.byref(p), None) == -1            # sample_size % 128
     p.sample_size = 384
     assert lib.ha_attn_fwd(C.byref(p), None) == -1            # more sampled rows than keys
+    p.sample_size = 128
+    p.sample_logw = dummy
+    assert lib.ha_attn_fwd(C.byref(p), None) == -1            # log weights without the dropped-slot mask
+    p.sample_logw = None
+    assert lib.ha_sample_weights(dummy, None, 1, 200, 128, 128, 0, dummy, dummy, dummy, None) == -1   # rows % 128
+    assert lib.ha_sample_weights(dummy, None, 1, 256, 128, 384, 0, dummy, dummy, dummy, None) == -1   # more slots than rows
+    assert lib.ha_sample_weights(None, None, 0, 256, 128, 128, 0, None, None, None, None) == 0        # nothing to do
     c = _lib.CausalParams()
     c.dtype, c.B, c.H, c.n, c.d, c.dv, c.levels, c.block_size, c.sample_size, c.lsh_bits = 0, 1, 32, 131072, 64, 64, 6, 256, 256, 8
     rows = 32 * 131072

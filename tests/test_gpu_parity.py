@@ -185,6 +185,102 @@ def test_hyper_attn_explicit_sample_idx(ha):
         assert rel(g, w) < 2e-4
 
 
+# ------------------------------------------------------------------------- weighted (uniformly sampled) key columns
+def test_sample_weights_kernel(ha):
+    """dropped-slot masks bit-exact, log weights to fp32 rounding, against the oracle's restatement"""
+    torch.manual_seed(30)
+    for n, block, S, smooth in [(512, 256, 128, False), (640, 384, 256, True), (384, 256, 128, False), (1024, 128, 384, True)]:
+        segs = 3
+        ki = torch.stack([torch.randperm(n) for _ in range(segs)])
+        sidx = torch.stack([torch.randperm(n)[:S] for _ in range(segs)])
+        logw, mask = ha.sample_weights(dev(ki).int(), dev(sidx).int(), n, block, S, smooth)
+        for sg in range(segs):
+            m_want, l_want = O.sample_tile_weights(n, ki[sg], block, sidx[sg], smooth)
+            bits = ((mask[sg].cpu().long()[:, :, None] >> torch.arange(32)) & 1).bool().view(n // 128, S)
+            assert torch.equal(bits, m_want)
+            assert torch.allclose(logw[sg].cpu(), l_want, rtol=1e-6, atol=1e-6)
+    # default rows 0..S-1 when no sample_idx is given
+    logw, mask = ha.sample_weights(dev(ki).int(), None, 1024, 128, 384, True)
+    m_want, _ = O.sample_tile_weights(1024, ki[0], 128, torch.arange(384), True)
+    assert torch.equal(((mask[0].cpu().long()[:, :, None] >> torch.arange(32)) & 1).bool().view(8, 384), m_want)
+
+
+@pytest.mark.parametrize('cfg', [
+    # B, H, n, d, dv, block, sample, smooth, dtype
+    (1, 2, 512, 64, 64, 256, 128, False, torch.float32),     # CUDA-core kernels
+    (1, 2, 512, 64, 64, 256, 128, False, torch.bfloat16),    # tensor-core kernels, pipelined backward
+    (2, 1, 640, 64, 64, 256, 256, True, torch.bfloat16),
+    (1, 1, 768, 128, 128, 256, 256, False, torch.float16),   # tensor-core kernels, serial backward
+    (1, 2, 384, 64, 32, 128, 128, False, torch.bfloat16),    # dv != d -> CUDA-core backward
+])
+def test_hyper_attn_weighted_sampling_vs_oracle(ha, cfg):
+    """uniformly sampled key rows, own block excluded, importance-weighted: forward and backward.  With n this small
+    about half of the sampled slots fall inside the query tile's window, so the dropped-slot path is exercised."""
+    B, H, n, d, dv, block, sample, smooth, dtype = cfg
+    q, k, v, do, qi, ki = _hyper_case(B, H, n, d, dv, dtype, seed=31)
+    sidx = torch.stack([torch.randperm(n)[:sample] for _ in range(B * H)]).view(B, H, sample)
+    from hyperattention_b200 import _lib as L
+    flags = L.FLAG_BWD_REF_SMOOTH if smooth else 0
+    qg, kg, vg = [dev(t).requires_grad_() for t in (q, k, v)]
+    o, lse = ha.hyper_attn_func(T(qg), T(kg), T(vg), T(dev(qi)), T(dev(ki)), block, sample, None, smooth, dev(sidx), flags, True)
+    T(o).backward(dev(do))
+    qc, kc, vc = [t.float().requires_grad_() for t in (q, k, v)]
+    ow, lw = O.hyper_attn_func(T(qc), T(kc), T(vc), T(qi), T(ki), block, sample, None, smooth, sidx, False, True)
+    T(ow).backward(do.float())
+    t_out, t_grad = TOL[dtype]
+    assert rel(T(o), T(ow)) < t_out and rel(lse, lw) < t_out
+    for g, w in zip((qg.grad, kg.grad, vg.grad), (qc.grad, kc.grad, vc.grad)):
+        assert rel(g, w) < t_grad
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_weighted_sampling_of_every_key_is_exact_attention(ha, dtype):
+    """property: when the sample is ALL keys, every key is counted once (in the block or as a kept sample of weight 1),
+    so the estimator equals exact attention whatever the permutations are"""
+    B, H, n, d = 1, 2, 512, 64
+    q, k, v, do, qi, ki = _hyper_case(B, H, n, d, d, dtype, seed=32)
+    sidx = torch.stack([torch.randperm(n) for _ in range(B * H)]).view(B, H, n)
+    qg, kg, vg = [dev(t).requires_grad_() for t in (q, k, v)]
+    o, lse = ha.hyper_attn_func(T(qg), T(kg), T(vg), T(dev(qi)), T(dev(ki)), 256, n, None, False, dev(sidx), 0, True)
+    T(o).backward(dev(do))
+    qc, kc, vc = [t.float().requires_grad_() for t in (q, k, v)]
+    s = (qc @ kc.transpose(-1, -2)) * d ** -0.5
+    ow = torch.softmax(s, -1) @ vc
+    ow.backward(do.float())
+    t_out, t_grad = TOL[dtype]
+    assert rel(T(o), ow) < t_out and rel(lse, torch.logsumexp(s, -1)) < t_out
+    for g, w in zip((qg.grad, kg.grad, vg.grad), (qc.grad, kc.grad, vc.grad)):
+        assert rel(g, w) < t_grad
+
+
+def test_module_uniform_sampling_mode(ha):
+    """HyperAttention(sampling='uniform'): seeded draws are reproducible, distinct and in range; the output matches the
+    oracle fed with the same draws; the causal recursion runs with it"""
+    import hyperattention_b200 as hb
+    torch.manual_seed(33)
+    B, H, n, d = 1, 2, 1024, 64
+    q, k, v = [torch.randn(B, H, n, d).bfloat16() for _ in range(3)]
+    gen = torch.Generator(device='cuda')
+    gen.manual_seed(7)
+    mod = hb.HyperAttention(input_dim=d, block_size=128, sample_size=128, min_seq_len=256, sampling='uniform',
+                            sample_generator=gen, rng=torch.Generator().manual_seed(1)).cuda().to(dtype=torch.bfloat16)
+    o1, lse1 = mod(dev(q), dev(k), dev(v), return_lse=True)
+    sidx = mod.last_sample_idx.cpu().long()
+    assert sidx.shape == (B, H, 128) and sidx.min() >= 0 and sidx.max() < n
+    assert all(len(set(sidx[0, h].tolist())) == 128 for h in range(H))
+    gen.manual_seed(7)
+    o2, _ = mod(dev(q), dev(k), dev(v), return_lse=True)
+    assert torch.equal(o1, o2) and torch.equal(mod.last_sample_idx.cpu().long(), sidx)
+    proj = mod.lsh.proj_dir.detach().cpu()
+    qi = O.stable_argsort(O.lsh_hash(q, proj))
+    ki = O.stable_argsort(O.lsh_hash(k, proj))
+    ow, lw = O.hyper_attn_func(T(q.float()), T(k.float()), T(v.float()), T(qi), T(ki), 128, 128, None, False, sidx, False, True)
+    if not (O.lsh_tie_mask(q, proj).any() or O.lsh_tie_mask(k, proj).any()):
+        assert rel(o1, T(ow)) < TOL[torch.bfloat16][0] and rel(lse1.squeeze(-1), lw) < TOL[torch.bfloat16][0]
+    oc = mod(dev(q), dev(k), dev(v), causal=True)
+    assert oc.shape == (B, H, n, d) and torch.isfinite(oc.float()).all()
+
+
 @pytest.mark.parametrize('tag', ['plain', 'smooth', 'nosamp', 'd128'])
 def test_hyper_attn_golden_reference_kernels(ha, golden_dir, tag):
     """outputs of the reference's Triton kernels (fp16, interpreter) on their own inputs"""
