@@ -239,20 +239,19 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_fwd = t.tolist()
 
-    # end to end through the public API with host buffers: pinned H2D of q, k, v, do; D2H of o and the three gradients
-    outs = [torch.empty_like(t) for t in host]
+    # end to end through the public host-buffer API: pinned H2D of q, k, v, do and D2H of o and the three gradients every
+    # step, streamed over chunks of heads (copy-in, kernels and copy-out overlap; PCIe is full duplex)
+    from hyperattention_b200.host import HostStream
+    outs = tuple(torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in host)
+    hs = HostStream(mod)
     def e2e_step():
-        qd, kd, vd, dod = [t.to(dev, non_blocking=True) for t in host]
-        qd, kd, vd = [t.requires_grad_() for t in (qd, kd, vd)]
-        o = mod(qd, kd, vd, causal=causal)
-        grads = torch.autograd.grad(o, (qd, kd, vd), dod)
-        for dst, src in zip(outs, (o.detach(),) + grads):
-            dst.copy_(src, non_blocking=True)
+        hs.forward_backward(*host, causal=causal, out=outs)
     ms_e2e = timed(e2e_step, max(2, args.steps // 2), 2, sync_all)
     if dist is not None:
         t = torch.tensor([ms_e2e], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_e2e = t.item()
+    ha.check_device_status(dev)
     clocks = sampler.stop()
     bytes_io = sum(t.numel() * t.element_size() for t in host)
 
@@ -261,7 +260,8 @@ def main():
             'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic', 'config': config, 'fwd_ms': ms_fwd, 'fwd_tokens_per_s': n / (ms_fwd * 1e-3),
             'clocks': clocks, 'gpu_launches': int(launches),
             'e2e': {'value': n / (ms_e2e * 1e-3), 'unit': 'tokens/s', 'ms_per_step': ms_e2e, 'h2d_bytes_per_step': bytes_io,
-                    'd2h_bytes_per_step': bytes_io}}
+                    'd2h_bytes_per_step': bytes_io, 'api': 'hyperattention_b200.host.HostStream.forward_backward',
+                    'pcie_gbs_each_way': bytes_io / (ms_e2e * 1e-3) / 1e9}}
 
     if rank == 0 and not args.no_extras:
         line.update(extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev))
@@ -343,6 +343,15 @@ def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
     tc_fb = timed(c_fwd_bwd, 5, 2, sync)
     tc_f = timed(c_fwd, 5, 2, sync)
     out['causal_config2'] = {'fwd_ms': tc_f, 'fwd_bwd_ms': tc_fb, 'fwd_bwd_tokens_per_s': n / (tc_fb * 1e-3)}
+    # the same step with uniformly sampled, importance-weighted key columns (fresh draws every call)
+    if not causal:
+        umod = ha.HyperAttention(input_dim=d, lsh_num_projs=BITS, block_size=BLOCK, sample_size=SAMPLE, min_seq_len=MIN_SEQ,
+                                 rng=torch.Generator().manual_seed(1234), sampling='uniform').to(device=dev, dtype=torch.bfloat16)
+        def u_fwd_bwd():
+            oo = umod(q, k, v)
+            return torch.autograd.grad(oo, (q, k, v), do)
+        u_fwd_bwd()
+        out['uniform_sampling'] = {'fwd_bwd_ms': timed(u_fwd_bwd, 5, 2, sync)}
     # exact attention of the same shape: our sm_100a flash kernel and the library kernel behind torch SDPA
     with torch.no_grad():
         t_ours = timed(lambda: ops.flash_attn_func(T(qd), T(kd), T(vd), None, True), 2, 1, sync)

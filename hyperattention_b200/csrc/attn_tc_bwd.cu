@@ -120,7 +120,8 @@ struct BwdItem {
   int k_tile;
 };
 
-__device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item, int seg, int items_blk, int n_chunks, int tid) {
+__device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item, int seg, int items_blk, int n_chunks, int tid,
+                                              bool weighted) {
   BwdItem it;
   const bool hyper = p.mode == HA_MODE_HYPER;
   const int n_qt = (p.m_q + TILE - 1) / TILE;
@@ -156,7 +157,7 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
     it.qt_first = z * BWD_CHUNK;
     if (!hyper && (p.flags & HA_FLAG_CAUSAL)) it.qt_first = max(it.qt_first, it.k_tile);
     it.qt_count = min((z + 1) * BWD_CHUNK, n_qt) - it.qt_first;
-    if (hyper && p.sample_logw) {
+    if (hyper && weighted) {
       // weighted sampling: the weight and the dropped slots belong to SORTED query tiles, so walk those
       it.q_sorted = true;
       it.q_pos0 = it.qt_first * TILE;
@@ -177,7 +178,8 @@ __device__ __forceinline__ int bwd_q_row(const ha_attn_params& p, const BwdItem&
   return r < p.m_q ? r : -1;
 }
 
-template <typename T, int D, int DV>
+// WT: weighted sampling (sample_logw / sample_mask given); a template flag so that the plain instantiation carries none of it
+template <typename T, int D, int DV, bool WT>
 __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p, int items_blk, int n_chunks, int pf_dist) {
   using Cfg = BwdCfg<D, DV>;
   extern __shared__ uint8_t smem_raw[];
@@ -197,7 +199,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   const SegInfo si = seg_info(p, seg);
 
   // ---- decode the work item: key rows of this CTA and its list of query tiles ----
-  const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row);
+  const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row, WT);
   const int krow = me.krow, qt_first = me.qt_first, qt_count = me.qt_count, k_tile = me.k_tile;
   if (qt_count <= 0) return;     // uniform over the CTA; nothing allocated yet
   if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
@@ -252,7 +254,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     if (hyper && pf_dist > 0 && lin < (long long)gridDim.x * gridDim.y) {
       const int pseg = (int)(lin / gridDim.x), pitem = (int)(lin - (long long)pseg * gridDim.x);
       pf_si = seg_info(p, pseg);
-      const BwdItem nx = bwd_decode(p, pitem, pseg, items_blk, n_chunks, row);
+      const BwdItem nx = bwd_decode(p, pitem, pseg, items_blk, n_chunks, row, WT);
       if (pitem < items_blk || p.sample_idx) pf_k = nx.krow;   // default sampled rows (0..S-1) stay hot in L2 anyway
 #pragma unroll
       for (int i = 0; i < PF_TILES; ++i) pf_q[i] = bwd_q_row(p, nx, pseg, i, row);
@@ -313,20 +315,20 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   // P and dS of this thread's query row, its group's 64 key columns -> shared memory
   // weighted sampling (sampled items only): pair jj meets sorted query tile qt_first + jj; its log weight is added to
   // the scores and the dropped slots among this group's 64 key columns give p = 0
-  const bool weighted = hyper && p.sample_logw && item >= items_blk;
+  const bool weighted = WT && hyper && item >= items_blk;
   auto elementwise = [&](float lse2, float dlt, bool diag, int jj) {
     const int limit = diag ? row + 1 : TILE;
     uint32_t wm[2] = {0u, 0u};
     float bias2 = 0.f;
-    if (weighted) {
+    if (WT && weighted) {
       const long long qtile = (long long)seg * (p.m_q / TILE) + qt_first + jj;
       const uint32_t* mw = p.sample_mask + qtile * (p.sample_size / 32) + k_tile * 4 + wg * 2;
       wm[0] = mw[0];
       wm[1] = mw[1];
       bias2 = p.sample_logw[qtile] * LOG2E;
     }
-    const bool masked = diag || (wm[0] | wm[1]) != 0u;
-    const uint64_t sc2 = pack_f2(scale2, scale2), nlse = pack_f2(bias2 - lse2, bias2 - lse2);
+    const bool masked = diag || (WT && (wm[0] | wm[1]) != 0u);
+    const uint64_t sc2 = pack_f2(scale2, scale2), nlse = WT ? pack_f2(bias2 - lse2, bias2 - lse2) : pack_f2(-lse2, -lse2);
     const uint64_t scl = pack_f2(p.scale, p.scale), ndel = pack_f2(-dlt * p.scale, -dlt * p.scale);
     const int col0 = wg * 64;
 #pragma unroll
@@ -346,8 +348,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
           p0 = fast_exp2(p0);
           p1 = fast_exp2(p1);
           if (masked) {
-            if (col0 + c * 32 + i + e >= limit || ((wm[c] >> (i + e)) & 1u)) p0 = 0.f;
-            if (col0 + c * 32 + i + e + 1 >= limit || ((wm[c] >> (i + e + 1)) & 1u)) p1 = 0.f;
+            if (col0 + c * 32 + i + e >= limit || (WT && ((wm[c] >> (i + e)) & 1u))) p0 = 0.f;
+            if (col0 + c * 32 + i + e + 1 >= limit || (WT && ((wm[c] >> (i + e + 1)) & 1u))) p1 = 0.f;
           }
           // ds = p * (dp - delta) * scale
           unpack_f2(fmul2(pack_f2(p0, p1), ffma2(pack_u2(rp[i + e], rp[i + e + 1]), scl, ndel)), d0, d1);
@@ -540,7 +542,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   if (tid < 32) tmem_dealloc(tmem, 512);
 }
 
-template <typename T, int D, int DV>
+template <typename T, int D, int DV, bool WT>
 static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   using Cfg = BwdCfg<D, DV>;
   const long long segs = (long long)p.B * p.H * p.segs_per_head;
@@ -556,13 +558,13 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
     items = (long long)n_kt * n_chunks;
   }
   if (items > 0x7fffffffLL || segs > 65535) return HA_ERR_INVALID;
-  HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_bwd_kernel<T, D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
+  HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_bwd_kernel<T, D, DV, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
              "ha_attn_bwd smem attribute");
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int pf_dist = p.mode == HA_MODE_HYPER ? sms : 0;   // one CTA per SM is resident: the next wave is `sms` items away
-  attn_tc_bwd_kernel<T, D, DV><<<dim3((unsigned)items, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist);
+  attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)items, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist);
   HA_LAUNCHED("ha_attn_bwd (tcgen05)");
   return HA_OK;
 }
@@ -581,7 +583,7 @@ bool tc_bwd_supported(const ha_attn_params& p) {
 
 int tc_attn_bwd(const ha_attn_params& p, cudaStream_t st) {
 #define HA_BWD_CASE(TT, DD, DDV) \
-  if (p.d == DD && p.dv == DDV) return launch_bwd<TT, DD, DDV>(p, st);
+  if (p.d == DD && p.dv == DDV) return p.sample_logw ? launch_bwd<TT, DD, DDV, true>(p, st) : launch_bwd<TT, DD, DDV, false>(p, st);
   if (p.dtype == HA_BF16) {
     HA_BWD_CASE(__nv_bfloat16, 64, 64)
     HA_BWD_CASE(__nv_bfloat16, 128, 128)

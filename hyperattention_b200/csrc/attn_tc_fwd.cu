@@ -85,7 +85,8 @@ struct TileList {
   Window w;
 };
 
-template <typename T, int D, int DV>
+// WT: weighted sampling (sample_logw / sample_mask given); a template flag so that the plain instantiation carries none of it
+template <typename T, int D, int DV, bool WT>
 __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p, const int pf_dist) {
   using Cfg = FwdCfg<D, DV>;
   extern __shared__ uint8_t smem_raw[];
@@ -103,6 +104,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   const int seg = blockIdx.y;
   const SegInfo si = seg_info(p, seg);
   const uint32_t bar = smem_u32(&mma_bar);
+  HA_T_DECL(8)
 
   if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
   if (tid == 0) {
@@ -205,7 +207,6 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   const float scale2 = p.scale * 1.4426950408889634f;
   uint32_t phase = 0;
   bool failed = false;
-  HA_T_DECL(8)
 
   auto issue_s = [&](int stg, uint32_t t_s) {
 #pragma unroll
@@ -247,6 +248,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
     mma_commit(bar);
   }
   float alpha_prev = 0.f;
+  HA_T_MARK(7)
   for (int j = 0; j < tl.n_tiles; ++j) {
     HA_T_MARK(0)
     const int st = j & 1;
@@ -272,7 +274,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
     // weighted sampling: a sampled tile's scores get the tile's log weight, and its dropped slots are masked
     uint32_t wm[4] = {0u, 0u, 0u, 0u};
     float bias2 = 0.f;
-    if (hyper && p.sample_logw && j >= tl.n_blk) {
+    if (WT && hyper && j >= tl.n_blk) {
       const long long qtile = (long long)seg * n_qt + qt;
       const uint32_t* mw = p.sample_mask + qtile * (p.sample_size / 32) + (j - tl.n_blk) * 4;
       wm[0] = mw[0]; wm[1] = mw[1]; wm[2] = mw[2]; wm[3] = mw[3];
@@ -309,18 +311,18 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < limit && !((wm[c] >> i) & 1u)) m0 = fmaxf(m0, __uint_as_float(cur[i]));
+            if (c * 32 + i < limit && !(WT && ((wm[c] >> i) & 1u))) m0 = fmaxf(m0, __uint_as_float(cur[i]));
         }
         if (c + 1 < 4) tmem_ld_fence(nxt);
       }
       mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
     }
-    const float m_new = fmaxf(m_run, mx * scale2 + bias2);
+    const float m_new = fmaxf(m_run, WT ? mx * scale2 + bias2 : mx * scale2);
     const float m_use = m_new == -INFINITY ? 0.f : m_new;
     const float alpha = fast_exp2(m_run - m_use);   // m_run = -inf -> 0
     float psum;
     {
-      const uint64_t sc2 = pack_f2(scale2, scale2), negm = pack_f2(bias2 - m_use, bias2 - m_use);
+      const uint64_t sc2 = pack_f2(scale2, scale2), negm = WT ? pack_f2(bias2 - m_use, bias2 - m_use) : pack_f2(-m_use, -m_use);
       uint64_t ps_a = pack_f2(0.f, 0.f), ps_b = ps_a;
       uint32_t ra[32], rb[32];
       tmem_ld32(tS + lane_sel, ra);
@@ -340,10 +342,10 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
           unpack_f2(ffma2(pack_u2(cur[i + 2], cur[i + 3]), sc2, negm), p2, p3);
           p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
           if (masked) {
-            if (c * 32 + i >= limit || ((wm[c] >> i) & 1u)) p0 = 0.f;
-            if (c * 32 + i + 1 >= limit || ((wm[c] >> (i + 1)) & 1u)) p1 = 0.f;
-            if (c * 32 + i + 2 >= limit || ((wm[c] >> (i + 2)) & 1u)) p2 = 0.f;
-            if (c * 32 + i + 3 >= limit || ((wm[c] >> (i + 3)) & 1u)) p3 = 0.f;
+            if (c * 32 + i >= limit || (WT && ((wm[c] >> i) & 1u))) p0 = 0.f;
+            if (c * 32 + i + 1 >= limit || (WT && ((wm[c] >> (i + 1)) & 1u))) p1 = 0.f;
+            if (c * 32 + i + 2 >= limit || (WT && ((wm[c] >> (i + 2)) & 1u))) p2 = 0.f;
+            if (c * 32 + i + 3 >= limit || (WT && ((wm[c] >> (i + 3)) & 1u))) p3 = 0.f;
           }
           ps_a = fadd2(ps_a, pack_f2(p0, p1));
           ps_b = fadd2(ps_b, pack_f2(p2, p3));
@@ -466,7 +468,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   if (warp == 0) tmem_dealloc(tmem, Cfg::TMEM_COLS);
 }
 
-template <typename T, int D, int DV>
+template <typename T, int D, int DV, bool WT>
 static int launch_fwd(const ha_attn_params& p, cudaStream_t st) {
   using Cfg = FwdCfg<D, DV>;
   const long long segs = (long long)p.B * p.H * p.segs_per_head;
@@ -474,14 +476,14 @@ static int launch_fwd(const ha_attn_params& p, cudaStream_t st) {
   if (segs == 0 || n_qt == 0) return HA_OK;
   if (segs > 65535) return HA_ERR_INVALID;
   // per device, so set on every launch (one process may drive several GPUs)
-  HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_fwd_kernel<T, D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
+  HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_fwd_kernel<T, D, DV, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
              "ha_attn_fwd smem attribute");
   // CTAs resident at once (shared memory and TMEM allow two per SM at head dim 64, one otherwise) = prefetch distance
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int pf_dist = p.mode == HA_MODE_HYPER ? sms * (Cfg::TMEM_COLS == 256 ? 2 : 1) : 0;
-  attn_tc_fwd_kernel<T, D, DV><<<dim3(n_qt, (unsigned)segs), 128, Cfg::SMEM, st>>>(p, pf_dist);
+  attn_tc_fwd_kernel<T, D, DV, WT><<<dim3(n_qt, (unsigned)segs), 128, Cfg::SMEM, st>>>(p, pf_dist);
   HA_LAUNCHED("ha_attn_fwd (tcgen05)");
   return HA_OK;
 }
@@ -504,7 +506,7 @@ bool tc_supported(const ha_attn_params& p) {
 
 int tc_attn_fwd(const ha_attn_params& p, cudaStream_t st) {
 #define HA_FWD_CASE(TT, DD, DDV) \
-  if (p.d == DD && p.dv == DDV) return launch_fwd<TT, DD, DDV>(p, st);
+  if (p.d == DD && p.dv == DDV) return p.sample_logw ? launch_fwd<TT, DD, DDV, true>(p, st) : launch_fwd<TT, DD, DDV, false>(p, st);
   if (p.dtype == HA_BF16) {
     HA_FWD_CASE(__nv_bfloat16, 64, 64)
     HA_FWD_CASE(__nv_bfloat16, 128, 128)
