@@ -33,9 +33,42 @@ static int check_common(const ha_attn_params& p, bool backward) {
     return HA_ERR_INVALID;
   }
   if (backward) {
-    if (!p.d_o || !p.delta || !p.dq_acc || !p.dk_acc || !p.dv_acc) return HA_ERR_INVALID;
+    if (!p.d_o || !p.delta || !p.dq_acc) return HA_ERR_INVALID;
+    if (p.dk_out || p.dv_out) {
+      // direct dK/dV: hyper pattern only (one work item owns a key tile's block part), both outputs, slot buffers if sampled
+      if (!p.dk_out || !p.dv_out || p.mode != HA_MODE_HYPER) return HA_ERR_INVALID;
+      if (p.sample_size > 0 && (!p.dk_sacc || !p.dv_sacc)) return HA_ERR_INVALID;
+      if ((uintptr_t)p.dk_out % 16 != 0 || (uintptr_t)p.dv_out % 16 != 0) return HA_ERR_INVALID;
+    } else if (!p.dk_acc || !p.dv_acc) {
+      return HA_ERR_INVALID;
+    }
   }
   return HA_OK;
+}
+
+template <typename T>
+__global__ void bwd_finish_kernel(const ha_attn_params p, long long total) {
+  // one thread per (segment, slot, 8 elements of dk | dv)
+  const int cpr_k = p.d / 8, cpr = cpr_k + p.dv / 8;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = (int)(i % cpr);
+  const long long ss = i / cpr;
+  const int slot = (int)(ss % p.sample_size), seg = (int)(ss / p.sample_size);
+  const SegInfo si = seg_info(p, seg);
+  const int row = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + slot] : slot;
+  const long long out_row = ((long long)(si.b * p.H + si.h)) * p.n + si.k_row0 + row;
+  const bool is_k = c < cpr_k;
+  const int w = is_k ? p.d : p.dv, e0 = (is_k ? c : c - cpr_k) * 8;
+  T* out = (is_k ? (T*)p.dk_out : (T*)p.dv_out) + out_row * w + e0;
+  const float* acc = (is_k ? p.dk_sacc : p.dv_sacc) + ((long long)seg * p.sample_size + slot) * w + e0;
+  uint4 raw = *reinterpret_cast<const uint4*>(out);
+  T* v = reinterpret_cast<T*>(&raw);
+  const float4 a0 = *reinterpret_cast<const float4*>(acc), a1 = *reinterpret_cast<const float4*>(acc + 4);
+  const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = from_f32<T>(to_f32<T>(v[j]) + a[j]);
+  *reinterpret_cast<uint4*>(out) = raw;
 }
 }  // namespace ha
 
@@ -58,7 +91,29 @@ int ha_attn_bwd(const ha_attn_params* p, void* stream) {
   if (rc != HA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(*p)) return tc_attn_bwd(*p, st);
+  if (p->dk_out) return HA_ERR_INVALID;   // direct dK/dV exists on the tensor-core kernel only
   return simt_attn_bwd(*p, st);
+}
+
+int ha_attn_bwd_uses_tensor_cores(const ha_attn_params* p) {
+  if (!p || !p->d_o) return 0;
+  return (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(*p)) ? 1 : 0;
+}
+
+int ha_attn_bwd_finish(const ha_attn_params* p, void* stream) {
+  if (!p) return HA_ERR_INVALID;
+  int rc = check_common(*p, true);
+  if (rc != HA_OK) return rc;
+  if (!p->dk_out || p->dtype == HA_FP32 || p->d % 8 || p->dv % 8) return HA_ERR_INVALID;
+  const long long segs = (long long)p->B * p->H * p->segs_per_head;
+  const long long total = segs * p->sample_size * (p->d / 8 + p->dv / 8);
+  if (total == 0) return HA_OK;
+  if ((total + 255) / 256 > 0x7fffffffLL) return HA_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (p->dtype == HA_BF16) bwd_finish_kernel<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(*p, total);
+  else bwd_finish_kernel<__half><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(*p, total);
+  HA_LAUNCHED("ha_attn_bwd_finish");
+  return HA_OK;
 }
 
 }  // extern "C"

@@ -111,6 +111,27 @@ __device__ __forceinline__ void reduce_rows(uint8_t* stage, uint32_t tmem_addr, 
   __syncwarp();
 }
 
+// NC fp32 values of the thread's TMEM lane -> NC values of type T stored at columns [0, NC) of global row my_row
+// (16-byte stores; a thread writes NC*2 contiguous bytes, whole 32-byte sectors)
+template <typename T, int NC>
+__device__ __forceinline__ void store_rows(uint32_t tmem_addr, T* __restrict__ base, int64_t row_stride, int my_row) {
+#pragma unroll
+  for (int c = 0; c < NC / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld32(tmem_addr + c * 32, r);
+    tmem_ld_fence(r);
+    if (my_row >= 0) {
+      uint4* dst = reinterpret_cast<uint4*>(base + (int64_t)my_row * row_stride + c * 32);
+#pragma unroll
+      for (int i = 0; i < 32; i += 8)
+        dst[i >> 3] = make_uint4(pack2<T>(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                                 pack2<T>(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                                 pack2<T>(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                                 pack2<T>(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+    }
+  }
+}
+
 // One work item: the key rows of a CTA and its list of query tiles.
 struct BwdItem {
   int krow;                  // local key row fetched / owned by thread tid (-1: none)
@@ -530,10 +551,25 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     // dK / dV rows of this key tile (lanes = keys) -> reductions into the accumulators, one column half per group;
     // the staging rows are private per warp, so consecutive reductions can share them
     __syncthreads();
-    float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
-    float* dv_base = p.dv_acc + (head0 + si.k_row0) * DV;
-    reduce_rows<DV / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, krow, row);
-    reduce_rows<D / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, krow, row);
+    if (p.dk_out == nullptr) {
+      float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
+      float* dv_base = p.dv_acc + (head0 + si.k_row0) * DV;
+      reduce_rows<DV / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, krow, row);
+      reduce_rows<D / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, krow, row);
+    } else if (item < items_blk) {
+      // direct dK/dV: this item holds the complete block part of its 128 key rows -> stored once, in the tensors' dtype
+      T* dk_base = (T*)p.dk_out + (head0 + si.k_row0) * D;
+      T* dv_base = (T*)p.dv_out + (head0 + si.k_row0) * DV;
+      store_rows<T, DV / 2>(tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, krow);
+      store_rows<T, D / 2>(tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, krow);
+    } else {
+      // direct dK/dV, sampled item: partial sums go to the slot-indexed fp32 buffers (small enough to live in L2)
+      const int slot = k_tile * TILE + row;
+      float* dk_base = p.dk_sacc + (long long)seg * p.sample_size * D;
+      float* dv_base = p.dv_sacc + (long long)seg * p.sample_size * DV;
+      reduce_rows<DV / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, slot, row);
+      reduce_rows<D / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, slot, row);
+    }
   }
   HA_T_MARK(7)
   HA_T_DUMP(8, (int)(blockIdx.y * gridDim.x + blockIdx.x), tid == 0)

@@ -228,27 +228,21 @@ class HyperAttnFunc(torch.autograd.Function):
         B, n, H, d = q.shape
         dv = v.shape[-1]
         dev = q.device
-        acc = torch.zeros(B * H * n * (2 * d + dv), dtype=torch.float32, device=dev)
         delta = torch.empty(B, H, n, dtype=torch.float32, device=dev)
         lib = L.load()
         with torch.cuda.device(dev):
             rc = lib.ha_delta(_ptr(o), *_bhn(o), _ptr(do), *_bhn(do), B, H, n, dv, _dtype_id(q), _ptr(delta), _stream())
             L.check(rc, 'ha_delta')
-            hyper_bwd_launch(q, k, v, qi, ki, si if has_si else None, o, lse, do, delta, acc, block_size, sample_size, scale, flags,
-                             (logw, mask) if has_w else None)
-            grads = _cast_grads(lib, acc, q.dtype, B, H, n, d, dv)
+            grads = hyper_bwd(q, k, v, qi, ki, si if has_si else None, o, lse, do, delta, block_size, sample_size, scale, flags,
+                              (logw, mask) if has_w else None)
         return grads + (None,) * 9
 
 
-def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sample_size, scale, flags, weights=None):
-    """One ha_attn_bwd call (HA_MODE_HYPER) on [B, n, H, *] views; acc = zeroed fp32 buffer holding dq | dk | dv
-    accumulators ([B,H,n,d], [B,H,n,d], [B,H,n,dv] back to back).  Nothing else is launched."""
+def _bwd_params(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, scale, flags, weights):
     B, n, H, d = q.shape
-    dv = v.shape[-1]
-    r = B * H * n
     p = L.AttnParams()
     p.mode, p.dtype, p.flags = L.MODE_HYPER, _dtype_id(q), flags
-    p.B, p.H, p.n, p.d, p.dv = B, H, n, d, dv
+    p.B, p.H, p.n, p.d, p.dv = B, H, n, d, v.shape[-1]
     p.segs_per_head, p.span, p.q_off, p.k_off, p.m_q, p.m_k = 1, n, 0, 0, n, n
     p.block_size, p.sample_size, p.scale = block_size, sample_size, scale
     _fill_qkv(p, q, k, v)
@@ -259,10 +253,57 @@ def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sa
     p.d_o = _ptr(do)
     p.do_sb, p.do_sh, p.do_sn = _bhn(do)
     p.delta = _ptr(delta)
-    p.dq_acc, p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr()), C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
     p.status = _ptr(_status_word(q.device))
     if weights is not None:
         p.sample_logw, p.sample_mask = _ptr(weights[0]), _ptr(weights[1])
+    return p
+
+
+def hyper_bwd(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, scale, flags, weights=None, direct=None):
+    """Backward of the hyper pattern on [B, n, H, *] views: returns (dq, dk, dv) as [B, n, H, *] views in the input dtype.
+    On the tensor-core kernel dK/dV are stored directly (ha_attn_params.dk_out) unless direct=False; explicit sampled
+    rows that may repeat keep the fp32 accumulators."""
+    B, n, H, d = q.shape
+    dv = v.shape[-1]
+    r = B * H * n
+    dev = q.device
+    lib = L.load()
+    p = _bwd_params(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, scale, flags, weights)
+    if direct is None:
+        direct = si is None or weights is not None          # distinct sampled rows
+    if direct and lib.ha_attn_bwd_uses_tensor_cores(C.byref(p)) == 1:
+        dq_acc = torch.zeros(r * d, dtype=torch.float32, device=dev)
+        out = torch.empty(r * (d + dv), dtype=q.dtype, device=dev)
+        segs = B * H
+        sacc = torch.zeros(max(1, segs * sample_size * (d + dv)), dtype=torch.float32, device=dev)
+        p.dq_acc = _ptr(dq_acc)
+        p.dk_out, p.dv_out = C.c_void_p(out.data_ptr()), C.c_void_p(out.data_ptr() + out.element_size() * r * d)
+        p.dk_sacc, p.dv_sacc = C.c_void_p(sacc.data_ptr()), C.c_void_p(sacc.data_ptr() + 4 * segs * sample_size * d)
+        L.check(lib.ha_attn_bwd(C.byref(p), _stream()), 'ha_attn_bwd')
+        L.check(lib.ha_attn_bwd_finish(C.byref(p), _stream()), 'ha_attn_bwd_finish')
+        dq = torch.empty(r * d, dtype=q.dtype, device=dev)
+        L.check(lib.ha_cast_from_f32(_ptr(dq_acc), _ptr(dq), r * d, _DT[q.dtype], _stream()), 'ha_cast_from_f32')
+        return (dq.view(B, H, n, d).transpose(1, 2), out[:r * d].view(B, H, n, d).transpose(1, 2),
+                out[r * d:].view(B, H, n, dv).transpose(1, 2))
+    acc = torch.zeros(r * (2 * d + dv), dtype=torch.float32, device=dev)
+    p.dq_acc = C.c_void_p(acc.data_ptr())
+    p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
+    L.check(lib.ha_attn_bwd(C.byref(p), _stream()), 'ha_attn_bwd')
+    return _cast_grads(lib, acc, q.dtype, B, H, n, d, dv)
+
+
+def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sample_size, scale, flags, weights=None, direct_out=None):
+    """One ha_attn_bwd call (HA_MODE_HYPER) on [B, n, H, *] views and nothing else.  acc = zeroed fp32 buffer holding
+    dq | dk | dv accumulators ([B,H,n,d], [B,H,n,d], [B,H,n,dv] back to back); with direct_out = (out, sacc) -- `out` in
+    the input dtype holding dk | dv, `sacc` the zeroed fp32 slot buffers [B*H*S*(d+dv)] -- only the dq part of acc is used."""
+    B, n, H, d = q.shape
+    r = B * H * n
+    p = _bwd_params(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, scale, flags, weights)
+    p.dq_acc, p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr()), C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
+    if direct_out is not None:
+        out, sacc = direct_out
+        p.dk_out, p.dv_out = C.c_void_p(out.data_ptr()), C.c_void_p(out.data_ptr() + out.element_size() * r * d)
+        p.dk_sacc, p.dv_sacc = C.c_void_p(sacc.data_ptr()), C.c_void_p(sacc.data_ptr() + 4 * B * H * sample_size * d)
     rc = L.load().ha_attn_bwd(C.byref(p), _stream())
     L.check(rc, 'ha_attn_bwd')
 

@@ -143,10 +143,24 @@ typedef struct {
   int32_t* status;                 /* optional device status word (0 = ok) */
   const float* sample_logw;        /* optional [B*H*segs_per_head][m_q/128]: log weight of the kept sampled slots */
   const uint32_t* sample_mask;     /* optional [B*H*segs_per_head][m_q/128][sample_size/32]: bit s = slot s dropped */
+  /* backward, HA_MODE_HYPER on the tensor-core kernel only (ha_attn_bwd_uses_tensor_cores): direct dK/dV.  Every key
+   * row's block part is complete inside one work item, so it is stored straight into dk_out / dv_out (dtype rows,
+   * [B,H,n,d] / [B,H,n,dv] contiguous, every row of every segment written); the sampled rows' extra terms are summed in
+   * the small slot-indexed fp32 buffers dk_sacc / dv_sacc ([B*H*segs_per_head][sample_size][d] / [...][dv], zeroed by
+   * the caller) and added by ha_attn_bwd_finish.  dk_acc / dv_acc are not used then.  sample_idx rows must be distinct.
+   * Same arithmetic as the reference, whose sampled-column kernel adds onto the dk / dv its block kernel stored
+   * (src/hyper_attn_triton.py:399-506, :517-665). */
+  void *dk_out, *dv_out;
+  float *dk_sacc, *dv_sacc;
 } ha_attn_params;
 
 int ha_attn_fwd(const ha_attn_params* p, void* stream);
 int ha_attn_bwd(const ha_attn_params* p, void* stream);
+/* 1 if ha_attn_bwd would run these parameters on the tcgen05 kernel (the only one that takes dk_out / dv_out), else 0.
+ * Only dtype, head dims, flags, strides and pointer alignment are looked at. */
+int ha_attn_bwd_uses_tensor_cores(const ha_attn_params* p);
+/* After ha_attn_bwd with dk_out / dv_out: dk_out[row of slot s] += dk_sacc[s] (same for dv), in the tensors' dtype. */
+int ha_attn_bwd_finish(const ha_attn_params* p, void* stream);
 
 /* Weights of uniformly sampled key columns (no counterpart in the reference's code; its paper's estimator).
  * For every sorted query tile t of every segment: slot s of sample_idx is dropped (mask bit set) when that key's

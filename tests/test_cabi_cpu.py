@@ -32,7 +32,7 @@ def test_every_declared_symbol_is_exported(lib):
 def test_struct_layout_matches_header(lib):
     """sizes computed from the header's field lists with natural alignment"""
     from hyperattention_b200 import _lib
-    assert C.sizeof(_lib.AttnParams) == 17 * 4 + 4 + 3 * 8 + 9 * 8 + 3 * 8 + 8 + 3 * 8 + 3 * 8 + 8 + 3 * 8 + 4 * 8 + 8 + 2 * 8
+    assert C.sizeof(_lib.AttnParams) == 17 * 4 + 4 + 3 * 8 + 9 * 8 + 3 * 8 + 8 + 3 * 8 + 3 * 8 + 8 + 3 * 8 + 4 * 8 + 8 + 2 * 8 + 4 * 8
     assert C.sizeof(_lib.CausalParams) == 12 * 4 + 4 + 4 + 6 * 8 + 4 * 8 + 5 * 8
 
 
@@ -59,6 +59,21 @@ def test_argument_validation_without_a_gpu(lib):
     p.sample_logw = dummy
     assert lib.ha_attn_fwd(C.byref(p), None) == -1            # log weights without the dropped-slot mask
     p.sample_logw = None
+    p.d_o = p.delta = p.dq_acc = dummy
+    assert lib.ha_attn_bwd(C.byref(p), None) == -1            # neither accumulators nor direct outputs for dk / dv
+    p.dk_out = dummy
+    assert lib.ha_attn_bwd(C.byref(p), None) == -1            # dk_out without dv_out
+    p.dv_out = dummy
+    assert lib.ha_attn_bwd(C.byref(p), None) == -1            # sampled rows but no slot buffers
+    p.mode, p.dk_sacc, p.dv_sacc = _lib.MODE_FLASH, dummy, dummy
+    assert lib.ha_attn_bwd(C.byref(p), None) == -1            # direct dk / dv exists for the hyper pattern only
+    p.mode, p.scale = _lib.MODE_HYPER, 0.125
+    assert lib.ha_attn_bwd_uses_tensor_cores(C.byref(p)) == 1
+    p.flags = _lib.FLAG_FORCE_SIMT
+    assert lib.ha_attn_bwd_uses_tensor_cores(C.byref(p)) == 0
+    assert lib.ha_attn_bwd(C.byref(p), None) == -1            # ... and on the tensor-core kernel only
+    p.flags = 0
+    p.dk_out = p.dv_out = p.dk_sacc = p.dv_sacc = None
     assert lib.ha_sample_weights(dummy, None, 1, 200, 128, 128, 0, dummy, dummy, dummy, None) == -1   # rows % 128
     assert lib.ha_sample_weights(dummy, None, 1, 256, 128, 384, 0, dummy, dummy, dummy, None) == -1   # more slots than rows
     assert lib.ha_sample_weights(None, None, 0, 256, 128, 128, 0, None, None, None, None) == 0        # nothing to do

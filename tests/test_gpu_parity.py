@@ -281,6 +281,38 @@ def test_module_uniform_sampling_mode(ha):
     assert oc.shape == (B, H, n, d) and torch.isfinite(oc.float()).all()
 
 
+@pytest.mark.parametrize('cfg', [
+    # n, d, block, sample, smooth, weighted, dtype
+    (1024, 64, 256, 256, False, False, torch.bfloat16),
+    (640, 64, 256, 128, True, False, torch.float16),
+    (768, 128, 256, 256, False, False, torch.bfloat16),
+    (512, 64, 128, 0, False, False, torch.bfloat16),          # no sampled part: no slot buffers
+    (1024, 64, 256, 256, False, True, torch.bfloat16),
+])
+def test_direct_dk_dv_matches_fp32_accumulators(ha, cfg):
+    """the backward with dK/dV stored directly (+ slot buffers and the finish kernel) against the same kernel reducing
+    into fp32 accumulators: dq identical up to atomic order, dk/dv within one extra rounding of the storage dtype"""
+    from hyperattention_b200 import ops, _lib as L
+    n, d, block, sample, smooth, weighted, dtype = cfg
+    B, H = 1, 3
+    q, k, v, do, qi, ki = _hyper_case(B, H, n, d, d, dtype, seed=41)
+    sidx = torch.stack([torch.randperm(n)[:sample] for _ in range(B * H)]).view(B, H, sample) if weighted else None
+    flags = (L.FLAG_SMOOTH | L.FLAG_BWD_REF_SMOOTH) if smooth else 0
+    qd, kd, vd, dod = [T(dev(t)) for t in (q, k, v, do)]
+    o, lse = ha.hyper_attn_func(qd, kd, vd, T(dev(qi)), T(dev(ki)), block, sample, None, smooth,
+                                None if sidx is None else dev(sidx), flags & ~L.FLAG_SMOOTH, weighted)
+    qi32, ki32 = dev(qi).int().view(B * H, n), dev(ki).int().view(B * H, n)
+    si32 = None if sidx is None else dev(sidx).int().view(B * H, sample)
+    wts = ops.sample_weights(ki32, si32, n, block, sample, smooth) if weighted else None
+    delta = (o.float() * dod.float()).sum(-1).transpose(1, 2).contiguous()
+    args = (qd, kd, vd, qi32, ki32, si32, o, lse, dod, delta, block, sample, d ** -0.5, flags, wts)
+    direct = ops.hyper_bwd(*args, direct=True)
+    legacy = ops.hyper_bwd(*args, direct=False)
+    assert rel(direct[0], legacy[0]) < 1e-3
+    for g, w in zip(direct[1:], legacy[1:]):
+        assert g.dtype == dtype and rel(g, w) < 6e-3
+
+
 @pytest.mark.parametrize('tag', ['plain', 'smooth', 'nosamp', 'd128'])
 def test_hyper_attn_golden_reference_kernels(ha, golden_dir, tag):
     """outputs of the reference's Triton kernels (fp16, interpreter) on their own inputs"""
