@@ -46,7 +46,10 @@ template <int D, int DV> struct BwdCfg {
   static constexpr int MAXD = D > DV ? D : DV;
   static constexpr int STG_HALF = RedStage<MAXD / 2>::BYTES;
   static constexpr int OFF_STG = PIPE ? OFF_DS + P_BYTES : OFF_P;
-  static constexpr int SMEM = (OFF_STG + 2 * STG_HALF > OFF_DS + P_BYTES ? OFF_STG + 2 * STG_HALF : OFF_DS + P_BYTES) + 1024;
+  // second key tile of a paired block item (PIPE only): K, V of key tile 2b+1 next to those of 2b
+  static constexpr int OFF_K2 = (OFF_STG + 2 * STG_HALF > OFF_DS + P_BYTES ? OFF_STG + 2 * STG_HALF : OFF_DS + P_BYTES);
+  static constexpr int OFF_V2 = OFF_K2 + K_BYTES;
+  static constexpr int SMEM = OFF_K2 + (PIPE ? K_BYTES + V_BYTES : 0) + 1024;
   // TMEM columns: S [0,128), dP [128,256), dV [256,256+DV), dK; dQ: two buffers of its own (PIPE) or over S
   static constexpr int COL_S = 0, COL_DP = 128, COL_DV = 256, COL_DK = PIPE ? 320 : 384, COL_DQ = PIPE ? 384 : 0;
 };
@@ -135,6 +138,8 @@ __device__ __forceinline__ void store_rows(uint32_t tmem_addr, T* __restrict__ b
 // One work item: the key rows of a CTA and its list of query tiles.
 struct BwdItem {
   int krow;                  // local key row fetched / owned by thread tid (-1: none)
+  int krow2;                 // paired block item: row of the second key tile
+  bool paired;               // block item over BOTH key tiles of a 256-row block: pairs (A,Q0) (A,Q1) (B,Q0) (B,Q1)
   int qt_first, qt_count;    // natural-order query tiles [qt_first, qt_first + qt_count) ...
   bool q_sorted;             // ... or, when set, qt_count tiles of sorted positions starting at q_pos0 (modulo m_q)
   int q_pos0;
@@ -142,8 +147,10 @@ struct BwdItem {
 };
 
 __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item, int seg, int items_blk, int n_chunks, int tid,
-                                              bool weighted) {
+                                              bool weighted, bool paired) {
   BwdItem it;
+  it.krow2 = -1;
+  it.paired = false;
   const bool hyper = p.mode == HA_MODE_HYPER;
   const int n_qt = (p.m_q + TILE - 1) / TILE;
   it.krow = -1;
@@ -151,7 +158,16 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
   it.qt_count = 0;
   it.q_sorted = false;
   it.q_pos0 = 0;
-  if (hyper && item < items_blk) {
+  if (hyper && item < items_blk && paired) {
+    // block size 256, plain windows: key tiles 2b, 2b+1 and query tiles 2b, 2b+1 form four pairs
+    it.paired = true;
+    it.k_tile = 2 * item;
+    it.krow = p.k_idx[(long long)seg * p.m_k + it.k_tile * TILE + tid];
+    it.krow2 = p.k_idx[(long long)seg * p.m_k + (it.k_tile + 1) * TILE + tid];
+    it.q_sorted = true;
+    it.q_pos0 = it.k_tile * TILE;
+    it.qt_count = 4;
+  } else if (hyper && item < items_blk) {
     it.k_tile = item;
     it.krow = p.k_idx[(long long)seg * p.m_k + it.k_tile * TILE + tid];
     const int bs = (p.block_size + TILE - 1) / TILE;
@@ -191,7 +207,7 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
 __device__ __forceinline__ int bwd_q_row(const ha_attn_params& p, const BwdItem& it, int seg, int jj, int tid) {
   if (jj >= it.qt_count) return -1;
   if (it.q_sorted) {
-    int pos = it.q_pos0 + jj * TILE + tid;
+    int pos = it.q_pos0 + (it.paired ? (jj & 1) : jj) * TILE + tid;
     if (pos >= p.m_q) pos -= p.m_q;
     return p.q_idx[(long long)seg * p.m_q + pos];
   }
@@ -201,7 +217,8 @@ __device__ __forceinline__ int bwd_q_row(const ha_attn_params& p, const BwdItem&
 
 // WT: weighted sampling (sample_logw / sample_mask given); a template flag so that the plain instantiation carries none of it
 template <typename T, int D, int DV, bool WT>
-__global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p, int items_blk, int n_chunks, int pf_dist) {
+__global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p, int items_blk, int n_chunks, int pf_dist,
+                                                          int pair_blocks) {
   using Cfg = BwdCfg<D, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -220,7 +237,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   const SegInfo si = seg_info(p, seg);
 
   // ---- decode the work item: key rows of this CTA and its list of query tiles ----
-  const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row, WT);
+  const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row, WT, Cfg::PIPE && pair_blocks);
+  const bool paired = Cfg::PIPE && me.paired;
   const int krow = me.krow, qt_first = me.qt_first, qt_count = me.qt_count, k_tile = me.k_tile;
   if (qt_count <= 0) return;     // uniform over the CTA; nothing allocated yet
   if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
@@ -247,6 +265,10 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_K, kbase, p.k_sn, krow, qwarp, lane);
     else bwd_gather_tile<DV>(s_base + Cfg::OFF_V, vbase, p.v_sn, krow, qwarp, lane);
   };
+  auto fetch_kv2 = [&]() {   // paired block item: the second key tile
+    if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_K2, kbase, p.k_sn, me.krow2, qwarp, lane);
+    else bwd_gather_tile<DV>(s_base + Cfg::OFF_V2, vbase, p.v_sn, me.krow2, qwarp, lane);
+  };
   auto fetch_q = [&](int stage, int qr) {
     if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_Q + stage * Cfg::Q_BYTES, qbase, p.q_sn, qr, qwarp, lane);
     else bwd_gather_tile<DV>(s_base + Cfg::OFF_DO + stage * Cfg::DO_BYTES, gbase, p.do_sn, qr, qwarp, lane);
@@ -266,7 +288,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
 
   // ---- rows of the work item that runs pf_dist CTAs later: index loads now, L2 prefetches after the first pair ----
   constexpr int PF_TILES = 4;
-  int pf_k = -1, pf_q[PF_TILES];
+  int pf_k = -1, pf_k2 = -1, pf_q[PF_TILES];
 #pragma unroll
   for (int i = 0; i < PF_TILES; ++i) pf_q[i] = -1;
   SegInfo pf_si = si;
@@ -275,8 +297,9 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     if (hyper && pf_dist > 0 && lin < (long long)gridDim.x * gridDim.y) {
       const int pseg = (int)(lin / gridDim.x), pitem = (int)(lin - (long long)pseg * gridDim.x);
       pf_si = seg_info(p, pseg);
-      const BwdItem nx = bwd_decode(p, pitem, pseg, items_blk, n_chunks, row, WT);
+      const BwdItem nx = bwd_decode(p, pitem, pseg, items_blk, n_chunks, row, WT, Cfg::PIPE && pair_blocks);
       if (pitem < items_blk || p.sample_idx) pf_k = nx.krow;   // default sampled rows (0..S-1) stay hot in L2 anyway
+      pf_k2 = nx.krow2;
 #pragma unroll
       for (int i = 0; i < PF_TILES; ++i) pf_q[i] = bwd_q_row(p, nx, pseg, i, row);
     }
@@ -302,22 +325,25 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   HA_T_DECL(8)
 
   // S = Q K^T and dP = dO V^T of the query tile in stage `stg`
-  auto issue_mma1 = [&](int stg) {
+  auto issue_mma1 = [&](int stg, bool second = false) {
     const uint32_t sQ = s_base + Cfg::OFF_Q + stg * Cfg::Q_BYTES, sDO = s_base + Cfg::OFF_DO + stg * Cfg::DO_BYTES;
+    const uint32_t sK = s_base + (second ? Cfg::OFF_K2 : Cfg::OFF_K), sV = s_base + (second ? Cfg::OFF_V2 : Cfg::OFF_V);
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
       const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-      mma_ss(tS, smem_desc(sQ + off, 16, 1024), smem_desc(s_base + Cfg::OFF_K + off, 16, 1024), id_s, kk > 0);
+      mma_ss(tS, smem_desc(sQ + off, 16, 1024), smem_desc(sK + off, 16, 1024), id_s, kk > 0);
     }
 #pragma unroll
     for (int kk = 0; kk < DV / 16; ++kk) {
       const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-      mma_ss(tDP, smem_desc(sDO + off, 16, 1024), smem_desc(s_base + Cfg::OFF_V + off, 16, 1024), id_s, kk > 0);
+      mma_ss(tDP, smem_desc(sDO + off, 16, 1024), smem_desc(sV + off, 16, 1024), id_s, kk > 0);
     }
   };
   // dV += P^T dO, dK += dS^T Q, dQ = dS K for the query tile in stage `stg`
-  auto issue_mma2 = [&](int stg, uint32_t acc0, uint32_t t_dq) {
+  // acc0: dV / dK accumulate onto what TMEM holds; dq_acc: so does dQ (paired block item, second key tile)
+  auto issue_mma2 = [&](int stg, uint32_t acc0, uint32_t t_dq, bool second = false, uint32_t dq_acc = 0) {
     const uint32_t sQ = s_base + Cfg::OFF_Q + stg * Cfg::Q_BYTES, sDO = s_base + Cfg::OFF_DO + stg * Cfg::DO_BYTES;
+    const uint32_t sK = s_base + (second ? Cfg::OFF_K2 : Cfg::OFF_K);
 #pragma unroll
     for (int kk = 0; kk < TILE / 16; ++kk)
       mma_ss(tDV, smem_desc(s_base + Cfg::OFF_P + kk * 2048, TILE * 128, 1024), smem_desc(sDO + kk * 2048, TILE * 128, 1024), id_dv,
@@ -329,8 +355,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
 #pragma unroll
     for (int kk = 0; kk < TILE / 16; ++kk) {
       const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-      mma_ss(t_dq, smem_desc(s_base + Cfg::OFF_DS + off, 16, 1024), smem_desc(s_base + Cfg::OFF_K + kk * 2048, TILE * 128, 1024), id_dq,
-             kk > 0);
+      mma_ss(t_dq, smem_desc(s_base + Cfg::OFF_DS + off, 16, 1024), smem_desc(sK + kk * 2048, TILE * 128, 1024), id_dq,
+             dq_acc | (kk > 0));
     }
   };
   // P and dS of this thread's query row, its group's 64 key columns -> shared memory
@@ -387,13 +413,17 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     if (wg != 0) return;
     const uint16_t* pq = (const uint16_t*)p.q + pf_si.b * p.q_sb + pf_si.h * p.q_sh + pf_si.q_row0 * p.q_sn;
     const uint16_t* pg = (const uint16_t*)p.d_o + pf_si.b * p.do_sb + pf_si.h * p.do_sh + pf_si.q_row0 * p.do_sn;
-    if (pf_k >= 0) {
-      const uint16_t* pk = (const uint16_t*)p.k + pf_si.b * p.k_sb + pf_si.h * p.k_sh + (pf_si.k_row0 + pf_k) * p.k_sn;
-      const uint16_t* pv = (const uint16_t*)p.v + pf_si.b * p.v_sb + pf_si.h * p.v_sh + (pf_si.k_row0 + pf_k) * p.v_sn;
-      prefetch_l2(pk);
-      if (D > 64) prefetch_l2(pk + 64);
-      prefetch_l2(pv);
-      if (DV > 64) prefetch_l2(pv + 64);
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int kr = t == 0 ? pf_k : pf_k2;
+      if (kr >= 0) {
+        const uint16_t* pk = (const uint16_t*)p.k + pf_si.b * p.k_sb + pf_si.h * p.k_sh + (pf_si.k_row0 + kr) * p.k_sn;
+        const uint16_t* pv = (const uint16_t*)p.v + pf_si.b * p.v_sb + pf_si.h * p.v_sh + (pf_si.k_row0 + kr) * p.v_sn;
+        prefetch_l2(pk);
+        if (D > 64) prefetch_l2(pk + 64);
+        prefetch_l2(pv);
+        if (DV > 64) prefetch_l2(pv + 64);
+      }
     }
 #pragma unroll
     for (int i = 0; i < PF_TILES; ++i) {
@@ -406,6 +436,29 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     }
   };
   const bool diag_possible = !hyper && causal;
+  // dK / dV rows of a key tile (lanes = keys), one column half per thread group: fp32 reductions into the accumulators
+  // (staging rows are private per warp), or -- direct mode -- stored once in the tensors' dtype (block items, which hold
+  // the complete block part of their rows) / reduced into the slot-indexed fp32 buffers (sampled items)
+  auto drain_kv = [&](int kr) {
+    uint8_t* stg = smem + Cfg::OFF_STG + wg * Cfg::STG_HALF;
+    if (p.dk_out == nullptr) {
+      float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
+      float* dv_base = p.dv_acc + (head0 + si.k_row0) * DV;
+      reduce_rows<DV / 2>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr, row);
+      reduce_rows<D / 2>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr, row);
+    } else if (item < items_blk) {
+      T* dk_base = (T*)p.dk_out + (head0 + si.k_row0) * D;
+      T* dv_base = (T*)p.dv_out + (head0 + si.k_row0) * DV;
+      store_rows<T, DV / 2>(tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr);
+      store_rows<T, D / 2>(tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr);
+    } else {
+      const int slot = k_tile * TILE + row;
+      float* dk_base = p.dk_sacc + (long long)seg * p.sample_size * D;
+      float* dv_base = p.dv_sacc + (long long)seg * p.sample_size * DV;
+      reduce_rows<DV / 2>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, slot, row);
+      reduce_rows<D / 2>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, slot, row);
+    }
+  };
 
   if constexpr (Cfg::PIPE) {
     // ------------------------------------------------------------------------------------------------------------
@@ -417,6 +470,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     if (qt_count > 1) {                       // query tile 1 goes into stage 1 right away
       fetch_q(1, qrow_next);
     }
+    if (paired) fetch_kv2();                  // needed from pair 2 on
     cp_async_commit();
     float lse_next = INFINITY, delta_next = 0.f;
     if (qt_count > 1 && qrow_next >= 0) { lse_next = lse_base[qrow_next] * LOG2E; delta_next = delta_base[qrow_next]; }
@@ -441,12 +495,14 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       // stage st^1 is free now (its last reader was batch(jj-1)): fetch query tile jj+1 (tile 1 is already there)
       int qrow_after = -1;
       float lse_after = INFINITY, delta_after = 0.f;
-      if (jj >= 1 && jj + 1 < qt_count) fetch_q(st ^ 1, qrow_next);
+      if (!paired && jj >= 1 && jj + 1 < qt_count) fetch_q(st ^ 1, qrow_next);   // (a paired item keeps both tiles)
       cp_async_commit();
       if (jj + 2 < qt_count) {
         qrow_after = q_row(jj + 2);
       }
       HA_T_MARK(2)
+      // paired block item: the first key tile's dV / dK are final once pair 1 is through; pair 2 starts them afresh
+      if (paired && jj == 2) drain_kv(krow);
       elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile, jj);
       HA_T_MARK(3)
       cp_async_wait<0>();                     // query tile jj+1 has landed
@@ -455,13 +511,19 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       __syncthreads();
       tc_fence_after();
       if (tid == 0) {
-        issue_mma2(st, jj > 0, tDQ + (jj & 1) * D);
-        if (jj + 1 < qt_count) issue_mma1(st ^ 1);
+        if (paired) {
+          // dV / dK restart with each key tile; dQ of a query tile sums over both key tiles in its own TMEM buffer
+          issue_mma2(st, jj & 1, tDQ + (jj & 1) * D, jj >= 2, jj >= 2 ? 1u : 0u);
+          if (jj + 1 < qt_count) issue_mma1(st ^ 1, jj + 1 >= 2);
+        } else {
+          issue_mma2(st, jj > 0, tDQ + (jj & 1) * D);
+          if (jj + 1 < qt_count) issue_mma1(st ^ 1);
+        }
         mma_commit(bar);
       }
       HA_T_MARK(4)
-      // underneath the batch: dQ of the previous pair
-      if (jj >= 1)
+      // underneath the batch: dQ of the previous pair (paired item: of query tile 0, complete after pair 2)
+      if (jj >= 1 && (!paired || jj == 3))
         reduce_rows<D / 2>(sSTG + wg * Cfg::STG_HALF, tDQ + ((jj - 1) & 1) * D + lane_sel + wg * (D / 2), dq_base + wg * (D / 2), D,
                            qrow_prev, row);
       HA_T_MARK(5)
@@ -548,28 +610,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   if (failed) {
     if (tid == 0 && p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
   } else {
-    // dK / dV rows of this key tile (lanes = keys) -> reductions into the accumulators, one column half per group;
-    // the staging rows are private per warp, so consecutive reductions can share them
     __syncthreads();
-    if (p.dk_out == nullptr) {
-      float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
-      float* dv_base = p.dv_acc + (head0 + si.k_row0) * DV;
-      reduce_rows<DV / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, krow, row);
-      reduce_rows<D / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, krow, row);
-    } else if (item < items_blk) {
-      // direct dK/dV: this item holds the complete block part of its 128 key rows -> stored once, in the tensors' dtype
-      T* dk_base = (T*)p.dk_out + (head0 + si.k_row0) * D;
-      T* dv_base = (T*)p.dv_out + (head0 + si.k_row0) * DV;
-      store_rows<T, DV / 2>(tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, krow);
-      store_rows<T, D / 2>(tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, krow);
-    } else {
-      // direct dK/dV, sampled item: partial sums go to the slot-indexed fp32 buffers (small enough to live in L2)
-      const int slot = k_tile * TILE + row;
-      float* dk_base = p.dk_sacc + (long long)seg * p.sample_size * D;
-      float* dv_base = p.dv_sacc + (long long)seg * p.sample_size * DV;
-      reduce_rows<DV / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, slot, row);
-      reduce_rows<D / 2>(smem + Cfg::OFF_STG + wg * Cfg::STG_HALF, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, slot, row);
-    }
+    drain_kv(paired ? me.krow2 : krow);
   }
   HA_T_MARK(7)
   HA_T_DUMP(8, (int)(blockIdx.y * gridDim.x + blockIdx.x), tid == 0)
@@ -587,9 +629,12 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   const int n_chunks = (n_qt + BWD_CHUNK - 1) / BWD_CHUNK;
   long long items;
   int items_blk = 0;
+  // block size 256 with plain windows on whole blocks: one item per block (both key tiles, both query tiles)
+  const int pair_blocks = Cfg::PIPE && p.mode == HA_MODE_HYPER && !(p.flags & HA_FLAG_SMOOTH) && (p.block_size + TILE - 1) / TILE == 2 &&
+                          p.m_k % (2 * TILE) == 0;
   if (p.mode == HA_MODE_HYPER) {
-    items_blk = n_kt;
-    items = (long long)n_kt + (long long)(p.sample_size / TILE) * n_chunks;
+    items_blk = pair_blocks ? n_kt / 2 : n_kt;
+    items = (long long)items_blk + (long long)(p.sample_size / TILE) * n_chunks;
   } else {
     items = (long long)n_kt * n_chunks;
   }
@@ -600,7 +645,7 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int pf_dist = p.mode == HA_MODE_HYPER ? sms : 0;   // one CTA per SM is resident: the next wave is `sms` items away
-  attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)items, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist);
+  attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)items, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist, pair_blocks);
   HA_LAUNCHED("ha_attn_bwd (tcgen05)");
   return HA_OK;
 }
