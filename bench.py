@@ -308,7 +308,7 @@ def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
         delta = (o.float() * T(do).float()).sum(-1).transpose(1, 2).contiguous()
         # (as in the step: dq into the zeroed fp32 accumulator, dk/dv stored directly, sampled rows into the slot buffers)
         acc = torch.zeros(rows * d, dtype=torch.float32, device=dev)
-        out_kv = torch.empty(rows * 2 * d, dtype=q.dtype, device=dev)
+        out_kv = torch.empty(rows * 3 * d, dtype=q.dtype, device=dev)
         sacc = torch.zeros(hpg * SAMPLE * 2 * d, dtype=torch.float32, device=dev)
         bwd = lambda: ops.hyper_bwd_launch(T(qd), T(kd), T(vd), qi32, ki32, None, o, lse, T(do), delta, acc, BLOCK, SAMPLE, d ** -0.5, 0,
                                            None, (out_kv, sacc))
@@ -335,7 +335,7 @@ def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
                        'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s', 'frac': ach / peaks['bf16_tflops'],
                        'traffic': BWD_DRAM_BYTES_PER_ROW * rows if BWD_DRAM_BYTES_PER_ROW else None,
                        'peak_source': peaks['src'], 'launch_ms': t_bwd, 'algorithmic_flops_per_launch': fl_bwd,
-                       'algorithmic_bytes_per_launch': rows * (6 * d * 2 + d * 4 + 8)}
+                       'algorithmic_bytes_per_launch': rows * (7 * d * 2 + 8)}
     # the causal configuration (benchmark configuration 2) on the same tensors: times do not depend on the values
     def c_fwd():
         with torch.no_grad():

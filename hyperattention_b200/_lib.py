@@ -37,7 +37,7 @@ class AttnParams(C.Structure):
         ('delta', vp), ('dq_acc', vp), ('dk_acc', vp), ('dv_acc', vp),
         ('status', vp),
         ('sample_logw', vp), ('sample_mask', vp),
-        ('dk_out', vp), ('dv_out', vp), ('dk_sacc', vp), ('dv_sacc', vp),
+        ('dk_out', vp), ('dv_out', vp), ('dk_sacc', vp), ('dv_sacc', vp), ('dq_out', vp),
     ]
 
 
@@ -65,7 +65,7 @@ SIGNATURES = {
     'ha_gather_rows': (C.c_int, [vp, i64, i64, i64, i32, i32, i32, i32, vp, i32, vp, vp]),
     'ha_attn_fwd': (C.c_int, [C.POINTER(AttnParams), vp]),
     'ha_attn_bwd': (C.c_int, [C.POINTER(AttnParams), vp]),
-    'ha_attn_bwd_uses_tensor_cores': (C.c_int, [C.POINTER(AttnParams)]),
+    'ha_attn_bwd_direct_level': (C.c_int, [C.POINTER(AttnParams)]),
     'ha_attn_bwd_finish': (C.c_int, [C.POINTER(AttnParams), vp]),
     'ha_sample_weights': (C.c_int, [vp, vp, i32, i32, i32, i32, i32, vp, vp, vp, vp]),
     'ha_delta': (C.c_int, [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, i32, vp, vp]),

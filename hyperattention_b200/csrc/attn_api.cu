@@ -39,8 +39,9 @@ static int check_common(const ha_attn_params& p, bool backward) {
       if (!p.dk_out || !p.dv_out || p.mode != HA_MODE_HYPER) return HA_ERR_INVALID;
       if (p.sample_size > 0 && (!p.dk_sacc || !p.dv_sacc)) return HA_ERR_INVALID;
       if ((uintptr_t)p.dk_out % 16 != 0 || (uintptr_t)p.dv_out % 16 != 0) return HA_ERR_INVALID;
-    } else if (!p.dk_acc || !p.dv_acc) {
-      return HA_ERR_INVALID;
+      if (p.dq_out && (uintptr_t)p.dq_out % 16 != 0) return HA_ERR_INVALID;
+    } else if (!p.dk_acc || !p.dv_acc || p.dq_out) {
+      return HA_ERR_INVALID;   // (dq_out comes with dk_out / dv_out only)
     }
   }
   return HA_OK;
@@ -91,13 +92,16 @@ int ha_attn_bwd(const ha_attn_params* p, void* stream) {
   if (rc != HA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   if (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(*p)) return tc_attn_bwd(*p, st);
-  if (p->dk_out) return HA_ERR_INVALID;   // direct dK/dV exists on the tensor-core kernel only
+  if (p->dk_out) return HA_ERR_INVALID;   // direct gradients exist on the tensor-core kernel only
   return simt_attn_bwd(*p, st);
 }
 
-int ha_attn_bwd_uses_tensor_cores(const ha_attn_params* p) {
-  if (!p || !p->d_o) return 0;
-  return (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(*p)) ? 1 : 0;
+int ha_attn_bwd_direct_level(const ha_attn_params* p) {
+  if (!p || !p->d_o || p->mode != HA_MODE_HYPER) return 0;
+  if ((p->flags & HA_FLAG_FORCE_SIMT) || !tc_bwd_supported(*p)) return 0;
+  const bool whole_blocks = !(p->flags & HA_FLAG_SMOOTH) && (p->block_size + TILE - 1) / TILE == 2 && p->m_k % (2 * TILE) == 0;
+  if (p->d == 64 && p->dv == 64 && whole_blocks && (p->sample_size == 0 || p->sample_size == 2 * TILE)) return 2;
+  return 1;
 }
 
 int ha_attn_bwd_finish(const ha_attn_params* p, void* stream) {

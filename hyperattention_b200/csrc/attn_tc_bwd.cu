@@ -81,9 +81,13 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // row, so a warp instruction adds whole 128-byte (NC = 32) or 256-byte (NC = 64) row slices.  `stage` holds 128 rows of
 // NC floats (16-byte chunk c of row r at position c ^ (r & 7) of its 128-byte group); a warp only touches the 32 rows of
 // its own lanes, so a warp-level sync suffices.  (A TMA bulk reduce-add per row was measured slower than this.)
-template <int NC>
+// MODE 0: red.add into fp32 rows.  MODE 1: plain fp32 store (first contribution to rows nobody has written yet).
+// MODE 2: last contribution: (fp32 row, if has_partial) + value -> stored in type T at `out` (same row / column layout).
+// Every mode maps (row, 16-byte chunk) to the same lane, so a store and a later reduction of one address come from one
+// thread, in program order.
+template <int NC, int MODE = 0, typename T = float>
 __device__ __forceinline__ void reduce_rows(uint8_t* stage, uint32_t tmem_addr, float* __restrict__ base, int64_t row_stride, int my_row,
-                                            int row) {
+                                            int row, T* __restrict__ out = nullptr, bool has_partial = true) {
   const int lane = row & 31, qwarp = row >> 5;
   float* srow = reinterpret_cast<float*>(stage) + row * NC;
 #pragma unroll
@@ -101,15 +105,41 @@ __device__ __forceinline__ void reduce_rows(uint8_t* stage, uint32_t tmem_addr, 
   __syncwarp();
   constexpr int CPR = NC / 4;               // 16-byte chunks per row: 8, 16 (or 32)
   constexpr int RPI = 32 / CPR;             // rows per warp instruction
+  constexpr int NI = 32 / RPI;
+  const int chunk = lane % CPR;
+  if constexpr (MODE == 2) {
+    // all loads of the partial sums first (independent, one DRAM round trip), then add, convert and store
+    int dst_rows[NI];
+    float4 part[NI];
 #pragma unroll
-  for (int i = 0; i < 32 / RPI; ++i) {
-    const int rl = i * RPI + lane / CPR;
-    const int dst_row = __shfl_sync(0xffffffffu, my_row, rl);
-    const int rr = qwarp * 32 + rl;
-    const int chunk = lane % CPR;
-    const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
-    const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + rr * NC + sw * 4);
-    if (dst_row >= 0) red_add_v4(base + (int64_t)dst_row * row_stride + chunk * 4, v.x, v.y, v.z, v.w);
+    for (int i = 0; i < NI; ++i) {
+      dst_rows[i] = __shfl_sync(0xffffffffu, my_row, i * RPI + lane / CPR);
+      part[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (has_partial && dst_rows[i] >= 0) part[i] = __ldcs(reinterpret_cast<const float4*>(base + (int64_t)dst_rows[i] * row_stride + chunk * 4));
+    }
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+      const int rr = qwarp * 32 + i * RPI + lane / CPR;
+      const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
+      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + rr * NC + sw * 4);
+      if (dst_rows[i] >= 0)
+        *reinterpret_cast<uint2*>(out + (int64_t)dst_rows[i] * row_stride + chunk * 4) =
+            make_uint2(pack2<T>(v.x + part[i].x, v.y + part[i].y), pack2<T>(v.z + part[i].z, v.w + part[i].w));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+      const int rl = i * RPI + lane / CPR;
+      const int dst_row = __shfl_sync(0xffffffffu, my_row, rl);
+      const int rr = qwarp * 32 + rl;
+      const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
+      const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + rr * NC + sw * 4);
+      if (dst_row >= 0) {
+        float* dst = base + (int64_t)dst_row * row_stride + chunk * 4;
+        if (MODE == 0) red_add_v4(dst, v.x, v.y, v.z, v.w);
+        else *reinterpret_cast<float4*>(dst) = v;
+      }
+    }
   }
   __syncwarp();
 }
@@ -140,6 +170,8 @@ struct BwdItem {
   int krow;                  // local key row fetched / owned by thread tid (-1: none)
   int krow2;                 // paired block item: row of the second key tile
   bool paired;               // block item over BOTH key tiles of a 256-row block: pairs (A,Q0) (A,Q1) (B,Q0) (B,Q1)
+  bool dual;                 // sampled item over BOTH sampled tiles: q_len pairs with tile A, then q_len pairs with tile B
+  int q_len;                 // query tiles of the item (dual: qt_count = 2 * q_len pairs)
   int qt_first, qt_count;    // natural-order query tiles [qt_first, qt_first + qt_count) ...
   bool q_sorted;             // ... or, when set, qt_count tiles of sorted positions starting at q_pos0 (modulo m_q)
   int q_pos0;
@@ -147,10 +179,12 @@ struct BwdItem {
 };
 
 __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item, int seg, int items_blk, int n_chunks, int tid,
-                                              bool weighted, bool paired) {
+                                              bool weighted, bool paired, bool dual) {
   BwdItem it;
   it.krow2 = -1;
   it.paired = false;
+  it.dual = false;
+  it.q_len = 0;
   const bool hyper = p.mode == HA_MODE_HYPER;
   const int n_qt = (p.m_q + TILE - 1) / TILE;
   it.krow = -1;
@@ -175,6 +209,20 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
     it.q_sorted = true;
     it.q_pos0 = w.first;
     it.qt_count = w.count / TILE;
+  } else if (hyper && dual) {
+    // both sampled tiles (slots 0..127 and 128..255) against a chunk of BWD_CHUNK / 2 query tiles
+    const int z = item - items_blk;
+    it.dual = true;
+    it.k_tile = 0;
+    it.krow = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + tid] : tid;
+    it.krow2 = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + TILE + tid] : TILE + tid;
+    it.qt_first = z * (BWD_CHUNK / 2);
+    it.q_len = min((z + 1) * (BWD_CHUNK / 2), n_qt) - it.qt_first;
+    it.qt_count = 2 * it.q_len;
+    if (weighted) {
+      it.q_sorted = true;
+      it.q_pos0 = it.qt_first * TILE;
+    }
   } else {
     const int i2 = hyper ? item - items_blk : item;
     int z;
@@ -206,6 +254,7 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
 // local query row of thread tid in list entry jj of an item (-1: none)
 __device__ __forceinline__ int bwd_q_row(const ha_attn_params& p, const BwdItem& it, int seg, int jj, int tid) {
   if (jj >= it.qt_count) return -1;
+  if (it.dual && jj >= it.q_len) jj -= it.q_len;
   if (it.q_sorted) {
     int pos = it.q_pos0 + (it.paired ? (jj & 1) : jj) * TILE + tid;
     if (pos >= p.m_q) pos -= p.m_q;
@@ -218,7 +267,7 @@ __device__ __forceinline__ int bwd_q_row(const ha_attn_params& p, const BwdItem&
 // WT: weighted sampling (sample_logw / sample_mask given); a template flag so that the plain instantiation carries none of it
 template <typename T, int D, int DV, bool WT>
 __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p, int items_blk, int n_chunks, int pf_dist,
-                                                          int pair_blocks) {
+                                                          int mode_bits, int item_base) {
   using Cfg = BwdCfg<D, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -233,12 +282,17 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   const bool hyper = p.mode == HA_MODE_HYPER;
   const bool causal = p.flags & HA_FLAG_CAUSAL;
   const int seg = blockIdx.y;
-  const int item = blockIdx.x;
+  const int item = blockIdx.x + item_base;
   const SegInfo si = seg_info(p, seg);
+  // mode_bits: 1 = block items cover whole 256-row blocks (paired); 2 = ordered dQ: the sampled items run in an earlier
+  // launch, as dual items (both sampled tiles; first tile stores its dQ rows into dq_acc, second adds), and the paired
+  // block items add their single contribution and write the final dq_out rows
+  const bool pair_blocks = Cfg::PIPE && (mode_bits & 1), ordered = Cfg::PIPE && (mode_bits & 2);
 
   // ---- decode the work item: key rows of this CTA and its list of query tiles ----
-  const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row, WT, Cfg::PIPE && pair_blocks);
-  const bool paired = Cfg::PIPE && me.paired;
+  const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row, WT, pair_blocks, ordered);
+  const bool paired = Cfg::PIPE && me.paired, dual = Cfg::PIPE && me.dual;
+  const int q_len = me.q_len;
   const int krow = me.krow, qt_first = me.qt_first, qt_count = me.qt_count, k_tile = me.k_tile;
   if (qt_count <= 0) return;     // uniform over the CTA; nothing allocated yet
   if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
@@ -295,9 +349,9 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   {
     const long long lin = (long long)blockIdx.y * gridDim.x + blockIdx.x + pf_dist;
     if (hyper && pf_dist > 0 && lin < (long long)gridDim.x * gridDim.y) {
-      const int pseg = (int)(lin / gridDim.x), pitem = (int)(lin - (long long)pseg * gridDim.x);
+      const int pseg = (int)(lin / gridDim.x), pitem = (int)(lin - (long long)pseg * gridDim.x) + item_base;
       pf_si = seg_info(p, pseg);
-      const BwdItem nx = bwd_decode(p, pitem, pseg, items_blk, n_chunks, row, WT, Cfg::PIPE && pair_blocks);
+      const BwdItem nx = bwd_decode(p, pitem, pseg, items_blk, n_chunks, row, WT, pair_blocks, ordered);
       if (pitem < items_blk || p.sample_idx) pf_k = nx.krow;   // default sampled rows (0..S-1) stay hot in L2 anyway
       pf_k2 = nx.krow2;
 #pragma unroll
@@ -368,8 +422,9 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     uint32_t wm[2] = {0u, 0u};
     float bias2 = 0.f;
     if (WT && weighted) {
-      const long long qtile = (long long)seg * (p.m_q / TILE) + qt_first + jj;
-      const uint32_t* mw = p.sample_mask + qtile * (p.sample_size / 32) + k_tile * 4 + wg * 2;
+      const bool second = dual && jj >= q_len;
+      const long long qtile = (long long)seg * (p.m_q / TILE) + qt_first + (second ? jj - q_len : jj);
+      const uint32_t* mw = p.sample_mask + qtile * (p.sample_size / 32) + (dual ? (second ? 1 : 0) : k_tile) * 4 + wg * 2;
       wm[0] = mw[0];
       wm[1] = mw[1];
       bias2 = p.sample_logw[qtile] * LOG2E;
@@ -439,7 +494,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   // dK / dV rows of a key tile (lanes = keys), one column half per thread group: fp32 reductions into the accumulators
   // (staging rows are private per warp), or -- direct mode -- stored once in the tensors' dtype (block items, which hold
   // the complete block part of their rows) / reduced into the slot-indexed fp32 buffers (sampled items)
-  auto drain_kv = [&](int kr) {
+  auto drain_kv = [&](int kr, int tile) {
     uint8_t* stg = smem + Cfg::OFF_STG + wg * Cfg::STG_HALF;
     if (p.dk_out == nullptr) {
       float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
@@ -452,7 +507,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       store_rows<T, DV / 2>(tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr);
       store_rows<T, D / 2>(tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr);
     } else {
-      const int slot = k_tile * TILE + row;
+      const int slot = tile * TILE + row;
       float* dk_base = p.dk_sacc + (long long)seg * p.sample_size * D;
       float* dv_base = p.dv_sacc + (long long)seg * p.sample_size * DV;
       reduce_rows<DV / 2>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, slot, row);
@@ -467,10 +522,24 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     // starts as soon as the batch has landed.
     // ------------------------------------------------------------------------------------------------------------
     uint8_t* sSTG = smem + Cfg::OFF_STG;
+    // dQ rows of pair jp (TMEM buffer jp & 1) -> global: fp32 reduction; in ordered mode a first-tile pair of a dual item
+    // stores, and a paired block item (last contribution, its launch runs after the sampled one) writes the final rows
+    auto drain_dq = [&](int jp, int qrow_of_pair) {
+      uint8_t* stg = sSTG + wg * Cfg::STG_HALF;
+      const uint32_t t_src = tDQ + (jp & 1) * D + lane_sel + wg * (D / 2);
+      float* dst = dq_base + wg * (D / 2);
+      if (ordered && paired)
+        reduce_rows<D / 2, 2, T>(stg, t_src, dst, D, qrow_of_pair, row, (T*)p.dq_out + (head0 + si.q_row0) * D + wg * (D / 2),
+                                 p.sample_size > 0);
+      else if (ordered && dual && jp < q_len)
+        reduce_rows<D / 2, 1>(stg, t_src, dst, D, qrow_of_pair, row);
+      else
+        reduce_rows<D / 2>(stg, t_src, dst, D, qrow_of_pair, row);
+    };
     if (qt_count > 1) {                       // query tile 1 goes into stage 1 right away
       fetch_q(1, qrow_next);
     }
-    if (paired) fetch_kv2();                  // needed from pair 2 on
+    if (paired || dual) fetch_kv2();          // the second key tile, needed from pair 2 (q_len) on
     cp_async_commit();
     float lse_next = INFINITY, delta_next = 0.f;
     if (qt_count > 1 && qrow_next >= 0) { lse_next = lse_base[qrow_next] * LOG2E; delta_next = delta_base[qrow_next]; }
@@ -502,7 +571,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       }
       HA_T_MARK(2)
       // paired block item: the first key tile's dV / dK are final once pair 1 is through; pair 2 starts them afresh
-      if (paired && jj == 2) drain_kv(krow);
+      if (paired && jj == 2) drain_kv(krow, k_tile);
+      if (dual && jj == q_len) drain_kv(krow, 0);
       elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile, jj);
       HA_T_MARK(3)
       cp_async_wait<0>();                     // query tile jj+1 has landed
@@ -515,6 +585,9 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
           // dV / dK restart with each key tile; dQ of a query tile sums over both key tiles in its own TMEM buffer
           issue_mma2(st, jj & 1, tDQ + (jj & 1) * D, jj >= 2, jj >= 2 ? 1u : 0u);
           if (jj + 1 < qt_count) issue_mma1(st ^ 1, jj + 1 >= 2);
+        } else if (dual) {
+          issue_mma2(st, jj != 0 && jj != q_len, tDQ + (jj & 1) * D, jj >= q_len);
+          if (jj + 1 < qt_count) issue_mma1(st ^ 1, jj + 1 >= q_len);
         } else {
           issue_mma2(st, jj > 0, tDQ + (jj & 1) * D);
           if (jj + 1 < qt_count) issue_mma1(st ^ 1);
@@ -523,11 +596,14 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       }
       HA_T_MARK(4)
       // underneath the batch: dQ of the previous pair (paired item: of query tile 0, complete after pair 2)
-      if (jj >= 1 && (!paired || jj == 3))
-        reduce_rows<D / 2>(sSTG + wg * Cfg::STG_HALF, tDQ + ((jj - 1) & 1) * D + lane_sel + wg * (D / 2), dq_base + wg * (D / 2), D,
-                           qrow_prev, row);
+      if (jj >= 1 && (!paired || jj == 3)) drain_dq(jj - 1, qrow_prev);
       HA_T_MARK(5)
       if (jj == 0) prefetch_next_item();
+      if (jj == 0 && ordered && paired && p.sample_size > 0) {
+        // the sampled launch's partial dQ rows of both query tiles: into L2 now, read by the final drains
+        if (qrow_cur >= 0) prefetch_l2(dq_base + (int64_t)qrow_cur * D + wg * (D / 2));
+        if (qrow_next >= 0) prefetch_l2(dq_base + (int64_t)qrow_next * D + wg * (D / 2));
+      }
       // rotate the per-tile registers; lse/delta of tile jj+2 are loaded here so that they arrive during the next pair
       qrow_prev = qrow_cur;
       qrow_cur = qrow_next;
@@ -546,9 +622,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       failed = __syncthreads_or(failed);
     }
     HA_T_MARK(6)
-    if (!failed)
-      reduce_rows<D / 2>(sSTG + wg * Cfg::STG_HALF, tDQ + ((qt_count - 1) & 1) * D + lane_sel + wg * (D / 2), dq_base + wg * (D / 2), D,
-                         qrow_prev, row);
+    if (!failed) drain_dq(qt_count - 1, qrow_prev);
   } else {
     // ------------------------------------------------------------------------------------------------------------
     // Serial schedule (head dim 128: TMEM has no room for a separate dQ buffer, shared memory none for a second stage)
@@ -611,7 +685,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     if (tid == 0 && p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
   } else {
     __syncthreads();
-    drain_kv(paired ? me.krow2 : krow);
+    drain_kv((paired || dual) ? me.krow2 : krow, dual ? 1 : k_tile);
   }
   HA_T_MARK(7)
   HA_T_DUMP(8, (int)(blockIdx.y * gridDim.x + blockIdx.x), tid == 0)
@@ -632,6 +706,10 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   // block size 256 with plain windows on whole blocks: one item per block (both key tiles, both query tiles)
   const int pair_blocks = Cfg::PIPE && p.mode == HA_MODE_HYPER && !(p.flags & HA_FLAG_SMOOTH) && (p.block_size + TILE - 1) / TILE == 2 &&
                           p.m_k % (2 * TILE) == 0;
+  // ordered dQ (dq_out given; tc_bwd_direct_level says when): sampled items first, then the block items
+  const bool ordered = p.dq_out != nullptr;
+  if (ordered && !(pair_blocks && (p.sample_size == 0 || p.sample_size == 2 * TILE))) return HA_ERR_INVALID;
+  const int n_chunks_dual = (n_qt + BWD_CHUNK / 2 - 1) / (BWD_CHUNK / 2);
   if (p.mode == HA_MODE_HYPER) {
     items_blk = pair_blocks ? n_kt / 2 : n_kt;
     items = (long long)items_blk + (long long)(p.sample_size / TILE) * n_chunks;
@@ -645,7 +723,16 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int pf_dist = p.mode == HA_MODE_HYPER ? sms : 0;   // one CTA per SM is resident: the next wave is `sms` items away
-  attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)items, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist, pair_blocks);
+  if (ordered) {
+    if (p.sample_size > 0) {
+      attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)n_chunks_dual, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist, 3,
+                                                                                                           items_blk);
+      HA_LAUNCHED("ha_attn_bwd (tcgen05, sampled items)");
+    }
+    attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)items_blk, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist, 3, 0);
+  } else {
+    attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)items, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist, pair_blocks, 0);
+  }
   HA_LAUNCHED("ha_attn_bwd (tcgen05)");
   return HA_OK;
 }

@@ -271,20 +271,25 @@ def hyper_bwd(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, s
     p = _bwd_params(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, scale, flags, weights)
     if direct is None:
         direct = si is None or weights is not None          # distinct sampled rows
-    if direct and lib.ha_attn_bwd_uses_tensor_cores(C.byref(p)) == 1:
-        dq_acc = torch.zeros(r * d, dtype=torch.float32, device=dev)
-        out = torch.empty(r * (d + dv), dtype=q.dtype, device=dev)
+    level = lib.ha_attn_bwd_direct_level(C.byref(p)) if direct else 0
+    if level >= 1:
         segs = B * H
+        out = torch.empty(r * (2 * d + dv), dtype=q.dtype, device=dev)           # dq | dk | dv
         sacc = torch.zeros(max(1, segs * sample_size * (d + dv)), dtype=torch.float32, device=dev)
+        # level 2: dq_acc is scratch the kernels initialise themselves; level 1: a zeroed accumulator, cast afterwards
+        dq_acc = (torch.empty if level == 2 else torch.zeros)(r * d, dtype=torch.float32, device=dev)
+        es = out.element_size()
         p.dq_acc = _ptr(dq_acc)
-        p.dk_out, p.dv_out = C.c_void_p(out.data_ptr()), C.c_void_p(out.data_ptr() + out.element_size() * r * d)
+        p.dk_out, p.dv_out = C.c_void_p(out.data_ptr() + es * r * d), C.c_void_p(out.data_ptr() + es * 2 * r * d)
         p.dk_sacc, p.dv_sacc = C.c_void_p(sacc.data_ptr()), C.c_void_p(sacc.data_ptr() + 4 * segs * sample_size * d)
+        if level == 2:
+            p.dq_out = _ptr(out)
         L.check(lib.ha_attn_bwd(C.byref(p), _stream()), 'ha_attn_bwd')
         L.check(lib.ha_attn_bwd_finish(C.byref(p), _stream()), 'ha_attn_bwd_finish')
-        dq = torch.empty(r * d, dtype=q.dtype, device=dev)
-        L.check(lib.ha_cast_from_f32(_ptr(dq_acc), _ptr(dq), r * d, _DT[q.dtype], _stream()), 'ha_cast_from_f32')
-        return (dq.view(B, H, n, d).transpose(1, 2), out[:r * d].view(B, H, n, d).transpose(1, 2),
-                out[r * d:].view(B, H, n, dv).transpose(1, 2))
+        if level == 1:
+            L.check(lib.ha_cast_from_f32(_ptr(dq_acc), _ptr(out), r * d, _DT[q.dtype], _stream()), 'ha_cast_from_f32')
+        return (out[:r * d].view(B, H, n, d).transpose(1, 2), out[r * d:2 * r * d].view(B, H, n, d).transpose(1, 2),
+                out[2 * r * d:].view(B, H, n, dv).transpose(1, 2))
     acc = torch.zeros(r * (2 * d + dv), dtype=torch.float32, device=dev)
     p.dq_acc = C.c_void_p(acc.data_ptr())
     p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
@@ -295,15 +300,19 @@ def hyper_bwd(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, s
 def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sample_size, scale, flags, weights=None, direct_out=None):
     """One ha_attn_bwd call (HA_MODE_HYPER) on [B, n, H, *] views and nothing else.  acc = zeroed fp32 buffer holding
     dq | dk | dv accumulators ([B,H,n,d], [B,H,n,d], [B,H,n,dv] back to back); with direct_out = (out, sacc) -- `out` in
-    the input dtype holding dk | dv, `sacc` the zeroed fp32 slot buffers [B*H*S*(d+dv)] -- only the dq part of acc is used."""
+    the input dtype holding dq | dk | dv, `sacc` the zeroed fp32 slot buffers [B*H*S*(d+dv)] -- only the dq part of acc is
+    used (as scratch where the library writes dq directly, else as the zeroed accumulator)."""
     B, n, H, d = q.shape
     r = B * H * n
     p = _bwd_params(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, scale, flags, weights)
     p.dq_acc, p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr()), C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
     if direct_out is not None:
         out, sacc = direct_out
-        p.dk_out, p.dv_out = C.c_void_p(out.data_ptr()), C.c_void_p(out.data_ptr() + out.element_size() * r * d)
+        es = out.element_size()
+        p.dk_out, p.dv_out = C.c_void_p(out.data_ptr() + es * r * d), C.c_void_p(out.data_ptr() + es * 2 * r * d)
         p.dk_sacc, p.dv_sacc = C.c_void_p(sacc.data_ptr()), C.c_void_p(sacc.data_ptr() + 4 * B * H * sample_size * d)
+        if L.load().ha_attn_bwd_direct_level(C.byref(p)) == 2:
+            p.dq_out = _ptr(out)
     rc = L.load().ha_attn_bwd(C.byref(p), _stream())
     L.check(rc, 'ha_attn_bwd')
 

@@ -152,13 +152,18 @@ typedef struct {
    * (src/hyper_attn_triton.py:399-506, :517-665). */
   void *dk_out, *dv_out;
   float *dk_sacc, *dv_sacc;
+  /* direct dQ (only where ha_attn_bwd_direct_level says 2; together with dk_out / dv_out): the sampled work items run
+   * first and leave their sum in dq_acc (fp32 scratch, need NOT be zeroed), the block items then add their single
+   * contribution per query row and write dq_out ([B,H,n,d] contiguous, dtype rows): no zero-fill, no cast pass. */
+  void* dq_out;
 } ha_attn_params;
 
 int ha_attn_fwd(const ha_attn_params* p, void* stream);
 int ha_attn_bwd(const ha_attn_params* p, void* stream);
-/* 1 if ha_attn_bwd would run these parameters on the tcgen05 kernel (the only one that takes dk_out / dv_out), else 0.
- * Only dtype, head dims, flags, strides and pointer alignment are looked at. */
-int ha_attn_bwd_uses_tensor_cores(const ha_attn_params* p);
+/* Which direct outputs ha_attn_bwd accepts for these parameters (dtype, head dims, flags, sizes, strides and pointer
+ * alignment are looked at): 0 = none (fp32 accumulators only), 1 = dk_out / dv_out, 2 = dq_out as well (head dims 64,
+ * block size 129..256 on whole blocks, plain windows, 0 or 256 sampled rows). */
+int ha_attn_bwd_direct_level(const ha_attn_params* p);
 /* After ha_attn_bwd with dk_out / dv_out: dk_out[row of slot s] += dk_sacc[s] (same for dv), in the tensors' dtype. */
 int ha_attn_bwd_finish(const ha_attn_params* p, void* stream);
 

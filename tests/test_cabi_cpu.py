@@ -32,7 +32,7 @@ def test_every_declared_symbol_is_exported(lib):
 def test_struct_layout_matches_header(lib):
     """sizes computed from the header's field lists with natural alignment"""
     from hyperattention_b200 import _lib
-    assert C.sizeof(_lib.AttnParams) == 17 * 4 + 4 + 3 * 8 + 9 * 8 + 3 * 8 + 8 + 3 * 8 + 3 * 8 + 8 + 3 * 8 + 4 * 8 + 8 + 2 * 8 + 4 * 8
+    assert C.sizeof(_lib.AttnParams) == 17 * 4 + 4 + 3 * 8 + 9 * 8 + 3 * 8 + 8 + 3 * 8 + 3 * 8 + 8 + 3 * 8 + 4 * 8 + 8 + 2 * 8 + 5 * 8
     assert C.sizeof(_lib.CausalParams) == 12 * 4 + 4 + 4 + 6 * 8 + 4 * 8 + 5 * 8
 
 
@@ -68,12 +68,22 @@ def test_argument_validation_without_a_gpu(lib):
     p.mode, p.dk_sacc, p.dv_sacc = _lib.MODE_FLASH, dummy, dummy
     assert lib.ha_attn_bwd(C.byref(p), None) == -1            # direct dk / dv exists for the hyper pattern only
     p.mode, p.scale = _lib.MODE_HYPER, 0.125
-    assert lib.ha_attn_bwd_uses_tensor_cores(C.byref(p)) == 1
+    assert lib.ha_attn_bwd_direct_level(C.byref(p)) == 1      # 128 sampled rows: dk / dv only
+    p.sample_size = 256
+    assert lib.ha_attn_bwd_direct_level(C.byref(p)) == 1      # block size 128: one key tile per block
+    p.block_size = 256
+    assert lib.ha_attn_bwd_direct_level(C.byref(p)) == 2
+    p.flags = _lib.FLAG_SMOOTH | _lib.FLAG_BWD_REF_SMOOTH
+    assert lib.ha_attn_bwd_direct_level(C.byref(p)) == 1
     p.flags = _lib.FLAG_FORCE_SIMT
-    assert lib.ha_attn_bwd_uses_tensor_cores(C.byref(p)) == 0
+    assert lib.ha_attn_bwd_direct_level(C.byref(p)) == 0
     assert lib.ha_attn_bwd(C.byref(p), None) == -1            # ... and on the tensor-core kernel only
-    p.flags = 0
+    p.flags, p.block_size, p.sample_size = 0, 128, 128
     p.dk_out = p.dv_out = p.dk_sacc = p.dv_sacc = None
+    p.dq_out = dummy
+    p.dk_acc = p.dv_acc = dummy
+    assert lib.ha_attn_bwd(C.byref(p), None) == -1            # dq_out without dk_out / dv_out
+    p.dq_out = p.dk_acc = p.dv_acc = None
     assert lib.ha_sample_weights(dummy, None, 1, 200, 128, 128, 0, dummy, dummy, dummy, None) == -1   # rows % 128
     assert lib.ha_sample_weights(dummy, None, 1, 256, 128, 384, 0, dummy, dummy, dummy, None) == -1   # more slots than rows
     assert lib.ha_sample_weights(None, None, 0, 256, 128, 128, 0, None, None, None, None) == 0        # nothing to do

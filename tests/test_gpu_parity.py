@@ -287,6 +287,9 @@ def test_module_uniform_sampling_mode(ha):
     (640, 64, 256, 128, True, False, torch.float16),
     (768, 128, 256, 256, False, False, torch.bfloat16),
     (512, 64, 128, 0, False, False, torch.bfloat16),          # no sampled part: no slot buffers
+    (512, 64, 256, 0, False, False, torch.bfloat16),          # direct dq without a sampled launch
+    (1152, 64, 256, 256, False, False, torch.float16),        # 9 query tiles: a last chunk of one tile; odd block count -> level 1
+    (2304, 64, 256, 256, False, False, torch.bfloat16),       # 18 query tiles: chunks of 8, 8, 2
     (1024, 64, 256, 256, False, True, torch.bfloat16),
 ])
 def test_direct_dk_dv_matches_fp32_accumulators(ha, cfg):
