@@ -50,10 +50,10 @@ class AngularLSH(torch.nn.Module):
         bin_ids = (mask * self.enc_vec).sum(-1)
         return self.perm[bin_ids]
 
-    def hash_cuda(self, mat):
+    def hash_cuda(self, mat, out=None):
         assert self.proj_dir.shape[:-2] == (1,) * (self.proj_dir.dim() - 2), 'one projection shared by all heads'
         assert mat.dtype == self.proj_dir.dtype, 'All three tensors must have the same type'
-        return ops.lsh_hash(mat, self.proj_f32())
+        return ops.lsh_hash(mat, self.proj_f32(), out)
 
     hash_triton = hash_cuda   # the name callers of the reference use
 
@@ -176,8 +176,12 @@ class HyperAttention(torch.nn.Module):
                                             scale, self.kernel_flags & L.FLAG_FORCE_SIMT)
         else:
             bits = self.lsh_num_projs
-            q_idx = ops.seg_sort(self.lsh.hash_cuda(query), bits).view(B, H, n_query)
-            k_idx = ops.seg_sort(self.lsh.hash_cuda(key), bits).view(B, H, key.shape[2])
+            # codes of q and k side by side: one segmented sort call covers both
+            codes = torch.empty(2, B, H, n_query, dtype=torch.int32, device=query.device)
+            self.lsh.hash_cuda(query, codes[0])
+            self.lsh.hash_cuda(key, codes[1])
+            idx = ops.seg_sort(codes.view(2 * B * H, n_query), bits)
+            q_idx, k_idx = idx[:B * H].view(B, H, n_query), idx[B * H:].view(B, H, n_query)
             sample_idx, weighted = None, False
             if self.sampling == 'uniform' and self.sample_size > 0:
                 # distinct uniform rows per (batch, head): the positions of the largest of n uniform variates

@@ -55,15 +55,17 @@ def _cuda(*ts):
 
 
 # ------------------------------------------------------------------------------------------------
-def lsh_hash(x, proj_f32):
+def lsh_hash(x, proj_f32, out=None):
     """codes int32 [B,H,n] for x [B,H,n,d]; proj_f32 float32 [d, r] on the same device
-    (replaces AngularLSHTriton.hash_triton, src/angular_lsh_triton.py:181-182)."""
+    (replaces AngularLSHTriton.hash_triton, src/angular_lsh_triton.py:181-182).  out: optional contiguous int32
+    [B,H,n] tensor to write into (lets q and k codes share one buffer and one sort call)."""
     _cuda(x, proj_f32)
     assert x.dim() == 4 and x.stride(-1) == 1
     B, H, n, d = x.shape
     assert proj_f32.dtype == torch.float32 and proj_f32.is_contiguous() and proj_f32.shape[0] == d
     r = proj_f32.shape[1]
-    codes = torch.empty(B, H, n, dtype=torch.int32, device=x.device)
+    codes = out if out is not None else torch.empty(B, H, n, dtype=torch.int32, device=x.device)
+    assert codes.shape == (B, H, n) and codes.dtype == torch.int32 and codes.is_contiguous() and codes.device == x.device
     with torch.cuda.device(x.device):
         rc = L.load().ha_lsh_hash(_ptr(x), x.stride(0), x.stride(1), x.stride(2), B, H, n, d, _dtype_id(x), _ptr(proj_f32), r,
                                   _ptr(codes), _stream())
@@ -217,12 +219,15 @@ class HyperAttnFunc(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, qi, ki, o, lse, si if si is not None else empty,
                               *(wts if wts is not None else (empty, empty)))
         ctx.cfg = (block_size, sample_size, scale, p.flags, si is not None, wts is not None)
+        ctx.set_materialize_grads(False)          # the gradient of lse is never used: no zero tensor for it
         return o, lse
 
     @staticmethod
     def backward(ctx, do, dlse_unused=None):
         q, k, v, qi, ki, o, lse, si, logw, mask = ctx.saved_tensors
         block_size, sample_size, scale, flags, has_si, has_w = ctx.cfg
+        if do is None:                            # only lse was used downstream: its gradient is dropped, as in the reference
+            return (None,) * 12
         if do.stride(-1) != 1:
             do = do.contiguous()
         B, n, H, d = q.shape
