@@ -91,8 +91,12 @@ int ha_attn_bwd(const ha_attn_params* p, void* stream) {
   int rc = check_common(*p, true);
   if (rc != HA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  if (p->flags & HA_FLAG_BWD_KV_INIT) {
+    // one work item must own a key tile's whole dK/dV: exact attention with a single chunk of query tiles
+    if (p->mode != HA_MODE_FLASH || p->m_q > 16 * TILE || p->dk_out) return HA_ERR_INVALID;
+  }
   if (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(*p)) return tc_attn_bwd(*p, st);
-  if (p->dk_out) return HA_ERR_INVALID;   // direct gradients exist on the tensor-core kernel only
+  if (p->dk_out || (p->flags & HA_FLAG_BWD_KV_INIT)) return HA_ERR_INVALID;   // tensor-core kernel only
   return simt_attn_bwd(*p, st);
 }
 

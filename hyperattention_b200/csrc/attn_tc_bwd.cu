@@ -499,8 +499,13 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     if (p.dk_out == nullptr) {
       float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
       float* dv_base = p.dv_acc + (head0 + si.k_row0) * DV;
-      reduce_rows<DV / 2>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr, row);
-      reduce_rows<D / 2>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr, row);
+      if (p.flags & HA_FLAG_BWD_KV_INIT) {   // this item is the only writer of its key rows: store, nothing to add to
+        reduce_rows<DV / 2, 1>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr, row);
+        reduce_rows<D / 2, 1>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr, row);
+      } else {
+        reduce_rows<DV / 2>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr, row);
+        reduce_rows<D / 2>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr, row);
+      }
     } else if (item < items_blk) {
       T* dk_base = (T*)p.dk_out + (head0 + si.k_row0) * D;
       T* dv_base = (T*)p.dv_out + (head0 + si.k_row0) * DV;

@@ -13,6 +13,8 @@
 
 namespace ha {
 
+bool tc_bwd_supported(const ha_attn_params& p);   // attn_tc_bwd.cu
+
 struct CausalPlan {
   long long rows;          // B*H*n
   long long idx_bytes;     // one depth's q_idx or k_idx
@@ -215,13 +217,25 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
   float* dk_acc = (float*)s;                 s += align256(pl.rows * p.d * 4);
   float* dv_acc = (float*)s;                 s += align256(pl.rows * p.dv * 4);
   float* delta = (float*)s;
-  HA_CUDA_OK(cudaMemsetAsync(dq_acc, 0, pl.rows * p.d * 4, st), "ha_causal_bwd memset");
-  HA_CUDA_OK(cudaMemsetAsync(dk_acc, 0, pl.rows * p.d * 4, st), "ha_causal_bwd memset");
-  HA_CUDA_OK(cudaMemsetAsync(dv_acc, 0, pl.rows * p.dv * 4, st), "ha_causal_bwd memset");
-
   ha_attn_params a;
   fill_attn(p, a);
   a.delta = delta; a.dq_acc = dq_acc; a.dk_acc = dk_acc; a.dv_acc = dv_acc;
+  // The leaves run first and cover every key row; on the tensor-core kernel one work item owns a key tile's whole
+  // dK/dV there (leaves of up to 2048 rows), so it stores them and the two accumulators need no zero-fill.
+  bool kv_init = false;
+  {
+    ha_attn_params probe = a;
+    probe.mode = HA_MODE_FLASH;
+    probe.flags = HA_FLAG_CAUSAL | (p.flags & HA_FLAG_FORCE_SIMT);
+    probe.segs_per_head = 1 << p.levels;
+    probe.span = pl.leaf; probe.m_q = pl.leaf; probe.m_k = pl.leaf;
+    kv_init = pl.leaf <= 16 * TILE && !(p.flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(probe);
+  }
+  HA_CUDA_OK(cudaMemsetAsync(dq_acc, 0, pl.rows * p.d * 4, st), "ha_causal_bwd memset");
+  if (!kv_init) {
+    HA_CUDA_OK(cudaMemsetAsync(dk_acc, 0, pl.rows * p.d * 4, st), "ha_causal_bwd memset");
+    HA_CUDA_OK(cudaMemsetAsync(dv_acc, 0, pl.rows * p.dv * 4, st), "ha_causal_bwd memset");
+  }
   // reference gradient convention: every part uses sum(o_part * dO) of its own output (its d(lse) is dropped);
   // exact convention: sum(o * dO) of the merged output, computed once
   bool fused_parts = false;
@@ -252,7 +266,7 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
   rc = part_delta(p.levels);
   if (rc != HA_OK) return rc;
   a.mode = HA_MODE_FLASH;
-  a.flags = HA_FLAG_CAUSAL | (p.flags & HA_FLAG_FORCE_SIMT);
+  a.flags = HA_FLAG_CAUSAL | (p.flags & HA_FLAG_FORCE_SIMT) | (kv_init ? HA_FLAG_BWD_KV_INIT : 0);
   a.segs_per_head = 1 << p.levels;
   a.span = pl.leaf; a.q_off = 0; a.k_off = 0; a.m_q = pl.leaf; a.m_k = pl.leaf;
   rc = ha_attn_bwd(&a, stream);
