@@ -130,6 +130,8 @@ def cpu_baseline(workload, n, d, heads_sample, total_heads, seed, target_seconds
     device-only attention callables replaced by the oracle's PyTorch Functions.  Timed on a sample of heads (one head
     first; if that is quick, as many heads as fit in about `target_seconds`) and scaled linearly to `total_heads`."""
     from oracle import hyper_oracle as O
+    # every host core: torchrun exports OMP_NUM_THREADS=1 to its ranks, which would make this a one-thread baseline
+    torch.set_num_threads(os.cpu_count() or 1)
     g = torch.Generator().manual_seed(1234)
     proj = torch.randn(1, 1, d, BITS, generator=g)
 
