@@ -178,7 +178,10 @@ def main():
     if args.impl == 'reference':
         if rank != 0:
             return
-        cb = cpu_baseline(args.workload, n, d, args.cpu_heads, heads, seed)
+        # every step is a bounded sample of the workload (whole heads at full length), sized so that the K steps together
+        # stay within about three minutes of host time
+        per_step = min(12.0, max(2.0, 150.0 / max(1, args.steps)))
+        cb = cpu_baseline(args.workload, n, d, args.cpu_heads, heads, seed, target_seconds=per_step)
         vals = [cb['value']]
         for _ in range(max(0, args.steps - 1)):
             vals.append(cpu_baseline(args.workload, n, d, cb['heads_sampled'], heads, seed)['value'])
