@@ -11,9 +11,34 @@
 // copies.
 #include "attn_index.cuh"
 
+#include <mutex>
+
 namespace ha {
 
 bool tc_bwd_supported(const ha_attn_params& p);   // attn_tc_bwd.cu
+
+// One helper stream and two events per device, created on first use and kept for the life of the process.
+struct SideStream { cudaStream_t stream; cudaEvent_t fork, join; };
+static SideStream* side_stream() {
+  static std::mutex mu;
+  static SideStream per_dev[64];
+  static bool ready[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ready[dev]) {
+    SideStream s;
+    // highest priority: its short kernels take the next free CTA slots instead of queueing behind a large grid
+    int prio_lo = 0, prio_hi = 0;
+    cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+    if (cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, prio_hi) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    per_dev[dev] = s;
+    ready[dev] = true;
+  }
+  return &per_dev[dev];
+}
 
 struct CausalPlan {
   long long rows;          // B*H*n
@@ -172,6 +197,30 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
   rc = ha_lsh_hash(p.k, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes_k, stream);
   if (rc != HA_OK) return rc;
 
+  // The sorts of every depth depend on the codes only: they run on a side stream (forked here, joined before the first
+  // rectangle) underneath the leaves' kernel, which does not need them.  36 short launches leave the critical path.
+  SideStream* side = side_stream();
+  cudaStream_t main_st = (cudaStream_t)stream;
+  if (side) {
+    HA_CUDA_OK(cudaEventRecord(side->fork, main_st), "ha_causal_fwd fork");
+    HA_CUDA_OK(cudaStreamWaitEvent(side->stream, side->fork, 0), "ha_causal_fwd fork");
+  }
+  void* sort_stream = side ? (void*)side->stream : stream;
+  int sort_rc = HA_OK;
+  for (int l = p.levels - 1; l >= 0 && sort_rc == HA_OK; --l) {
+    const int span = p.n >> l, m = span / 2;
+    sort_rc = ha_seg_sort(codes_q, p.B * p.H, p.n, span, m, m, p.lsh_bits, sv.q_idx(l), sort_ws, pl.sort_ws, sort_stream);
+    if (sort_rc == HA_OK)
+      sort_rc = ha_seg_sort(codes_k, p.B * p.H, p.n, span, 0, m, p.lsh_bits, sv.k_idx(l), sort_ws, pl.sort_ws, sort_stream);
+  }
+  if (side) {   // joined in every case, so that the caller's stream also orders after whatever the side stream holds
+    HA_CUDA_OK(cudaEventRecord(side->join, side->stream), "ha_causal_fwd join");
+  }
+  if (sort_rc != HA_OK) {
+    if (side) cudaStreamWaitEvent(main_st, side->join, 0);
+    return sort_rc;
+  }
+
   ha_attn_params a;
   fill_attn(p, a);
   // leaves: exact causal attention on 2^levels spans per head
@@ -181,14 +230,11 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
   a.span = pl.leaf; a.q_off = 0; a.k_off = 0; a.m_q = pl.leaf; a.m_k = pl.leaf;
   if (p.keep_parts) { a.part_o = sv.part_o(p.levels); a.part_lse = sv.part_lse(p.levels); }
   rc = ha_attn_fwd(&a, stream);
+  if (side) HA_CUDA_OK(cudaStreamWaitEvent(main_st, side->join, 0), "ha_causal_fwd join");
   if (rc != HA_OK) return rc;
 
   for (int l = p.levels - 1; l >= 0; --l) {
     const int span = p.n >> l, m = span / 2;
-    rc = ha_seg_sort(codes_q, p.B * p.H, p.n, span, m, m, p.lsh_bits, sv.q_idx(l), sort_ws, pl.sort_ws, stream);
-    if (rc != HA_OK) return rc;
-    rc = ha_seg_sort(codes_k, p.B * p.H, p.n, span, 0, m, p.lsh_bits, sv.k_idx(l), sort_ws, pl.sort_ws, stream);
-    if (rc != HA_OK) return rc;
     a.mode = HA_MODE_HYPER;
     a.flags = HA_FLAG_MERGE | (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_MERGE_EXACT | HA_FLAG_FORCE_SIMT));
     a.segs_per_head = 1 << l;
