@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_HERE, 'libhyperattn_b200.so')
 HA_OK = 0
 BF16, FP16, FP32 = 0, 1, 2
 MODE_HYPER, MODE_FLASH = 0, 1
-FLAG_CAUSAL, FLAG_SMOOTH, FLAG_MERGE, FLAG_MERGE_EXACT, FLAG_BWD_REF_SMOOTH, FLAG_FORCE_SIMT, FLAG_BWD_KV_INIT = 1, 2, 4, 8, 16, 32, 64
+FLAG_CAUSAL, FLAG_SMOOTH, FLAG_MERGE, FLAG_MERGE_EXACT, FLAG_BWD_REF_SMOOTH, FLAG_FORCE_SIMT, FLAG_BWD_KV_INIT, FLAG_NO_WS = 1, 2, 4, 8, 16, 32, 64, 128
 
 _STATUS = {-1: 'invalid argument (shape / stride / size not accepted)', -2: 'unsupported dtype',
            -3: 'workspace missing or too small', -4: 'CUDA runtime error', 1: 'device-side wait timed out',

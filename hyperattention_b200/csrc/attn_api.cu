@@ -5,6 +5,8 @@ namespace ha {
 int simt_attn_fwd(const ha_attn_params& p, cudaStream_t st);
 int simt_attn_bwd(const ha_attn_params& p, cudaStream_t st);
 int tc_attn_fwd(const ha_attn_params& p, cudaStream_t st);
+int ws_attn_fwd(const ha_attn_params& p, cudaStream_t st);
+bool ws_fwd_supported(const ha_attn_params& p);
 bool tc_supported(const ha_attn_params& p);
 bool tc_bwd_supported(const ha_attn_params& p);
 int tc_attn_bwd(const ha_attn_params& p, cudaStream_t st);
@@ -82,6 +84,7 @@ int ha_attn_fwd(const ha_attn_params* p, void* stream) {
   int rc = check_common(*p, false);
   if (rc != HA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  if (!(p->flags & HA_FLAG_FORCE_SIMT) && ws_fwd_supported(*p)) return ws_attn_fwd(*p, st);
   if (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_supported(*p)) return tc_attn_fwd(*p, st);
   return simt_attn_fwd(*p, st);
 }

@@ -44,6 +44,7 @@ enum {
   HA_FLAG_MERGE_EXACT = 8,   /* with MERGE: plain log-sum-exp combine instead of the reference's rounded formula */
   HA_FLAG_BWD_REF_SMOOTH = 16,/* backward + SMOOTH: enumerate pairs per key tile as the reference backward does */
   HA_FLAG_FORCE_SIMT = 32,   /* use the fp32 CUDA-core kernels even where a tensor-core kernel exists */
+  HA_FLAG_NO_WS = 128,       /* forward: keep the one-tile-per-CTA kernel where the persistent warp-specialised one applies */
   HA_FLAG_BWD_KV_INIT = 64   /* backward, HA_MODE_FLASH with m_q <= 2048 on the tensor-core kernel: dk_acc / dv_acc hold
                                 garbage; the launch stores (not adds) every key row of every segment */
 };

@@ -483,3 +483,17 @@ def test_launch_counter_moves(ha):
     before = ha.launch_count()
     ha.lsh_hash(torch.randn(1, 1, 128, 64, device='cuda'), torch.randn(64, 8, device='cuda'))
     assert ha.launch_count() == before + 1
+
+
+@pytest.mark.parametrize('cfg', [(2, 3, 1024, 256, 256, torch.bfloat16), (1, 2, 512, 200, 128, torch.float16), (1, 40, 2048, 256, 0, torch.bfloat16)])
+def test_persistent_forward_matches_one_tile_forward(ha, cfg):
+    """the persistent warp-specialised forward (block size 256, head dim 64) against the one-tile-per-CTA kernel on the
+    same inputs: same arithmetic in the same order per row, so outputs and lse are bit-identical.  The last case has
+    more work items (320) than SMs, so every CTA walks several items and the copy ring wraps."""
+    from hyperattention_b200 import _lib as L
+    B, H, n, block, sample, dtype = cfg
+    q, k, v, do, qi, ki = _hyper_case(B, H, n, 64, 64, dtype, seed=50)
+    args = (T(dev(q)), T(dev(k)), T(dev(v)), T(dev(qi)), T(dev(ki)), block, sample, None, False, None)
+    o1, l1 = ha.hyper_attn_func(*args, 0)
+    o2, l2 = ha.hyper_attn_func(*args, L.FLAG_NO_WS)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
