@@ -433,31 +433,57 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
         lse = l1 - __logf(c + 1.1920929e-07f);
       }
     }
-    if (p.part_o) {
-      // un-merged result of this call, staged over the (now idle) Q tile
-      uint8_t* st2 = smem + Cfg::OFF_Q;
-      __syncthreads();   // all S MMAs reading Q have completed (waited above); make the reuse explicit
+    if (merge) {
+      // merge (the causal schedule's rectangles): rows staged in shared memory and stored row-coalesced; measured faster
+      // here than per-thread row stores (two output tensors per tile and the read of the previous rows)
+      if (p.part_o) {
+        // un-merged result of this call, staged over the (now idle) Q tile
+        uint8_t* st2 = smem + Cfg::OFF_Q;
+        __syncthreads();   // all S MMAs reading Q have completed (waited above); make the reuse explicit
 #pragma unroll
-      for (int e = 0; e < DV; e += 2)
-        *reinterpret_cast<uint32_t*>(st2 + swz_off(TILE, tid, e)) = pack2<T>(o_acc[e] * inv, o_acc[e + 1] * inv);
-      __syncwarp();
-      uint16_t* pbase = (uint16_t*)p.part_o + si.b * p.o_sb + si.h * p.o_sh + si.q_row0 * p.o_sn;
-      scatter_tile<DV>(st2, pbase, p.o_sn, qrow, warp, lane);
-      if (p.part_lse && qrow >= 0) p.part_lse[lse_at] = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
-    }
+        for (int e = 0; e < DV; e += 2)
+          *reinterpret_cast<uint32_t*>(st2 + swz_off(TILE, tid, e)) = pack2<T>(o_acc[e] * inv, o_acc[e + 1] * inv);
+        __syncwarp();
+        uint16_t* pbase = (uint16_t*)p.part_o + si.b * p.o_sb + si.h * p.o_sh + si.q_row0 * p.o_sn;
+        scatter_tile<DV>(st2, pbase, p.o_sn, qrow, warp, lane);
+        if (p.part_lse && qrow >= 0) p.part_lse[lse_at] = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      }
 #pragma unroll
-    for (int e = 0; e < DV; e += 2) {
-      float a = o_acc[e] * inv, b = o_acc[e + 1] * inv;
-      uint32_t* slot = reinterpret_cast<uint32_t*>(stage + swz_off(TILE, tid, e));
-      if (merge) {
+      for (int e = 0; e < DV; e += 2) {
+        float a = o_acc[e] * inv, b = o_acc[e + 1] * inv;
+        uint32_t* slot = reinterpret_cast<uint32_t*>(stage + swz_off(TILE, tid, e));
         const float2 old = unpack2<T>(*slot);
         a = w1 * old.x + w2 * round_to<T>(a);
         b = w1 * old.y + w2 * round_to<T>(b);
+        *slot = pack2<T>(a, b);
       }
-      *slot = pack2<T>(a, b);
+      __syncwarp();
+      scatter_tile<DV>(stage, obase, p.o_sn, qrow, warp, lane);
+    } else {
+      // each thread stores its own row: DV contiguous elements in 16-byte pieces straight from registers (whole 32-byte
+      // sectors pair up in L2); much less code than staging, and this code runs once per tile
+      if (p.part_o && qrow >= 0) {
+        // un-merged result of this call
+        uint4* prow = reinterpret_cast<uint4*>((uint16_t*)p.part_o + si.b * p.o_sb + si.h * p.o_sh + (si.q_row0 + qrow) * p.o_sn);
+#pragma unroll
+        for (int e = 0; e < DV; e += 8)
+          prow[e >> 3] = make_uint4(pack2<T>(o_acc[e] * inv, o_acc[e + 1] * inv), pack2<T>(o_acc[e + 2] * inv, o_acc[e + 3] * inv),
+                                    pack2<T>(o_acc[e + 4] * inv, o_acc[e + 5] * inv), pack2<T>(o_acc[e + 6] * inv, o_acc[e + 7] * inv));
+        if (p.part_lse) p.part_lse[lse_at] = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      }
+      if (qrow >= 0) {
+        uint4* orow = reinterpret_cast<uint4*>(obase + (int64_t)qrow * p.o_sn);
+#pragma unroll
+        for (int e = 0; e < DV; e += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            w[h] = pack2<T>(o_acc[e + 2 * h] * inv, o_acc[e + 2 * h + 1] * inv);
+          }
+          orow[e >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
     }
-    __syncwarp();
-    scatter_tile<DV>(stage, obase, p.o_sn, qrow, warp, lane);
     if (qrow >= 0) p.lse[lse_at] = lse;
   }
 

@@ -26,8 +26,7 @@ constexpr int KV_STAGES = 4;
 constexpr int TILE_B = TILE * 64 * 2;                          // one 128 x 64 tile of 2-byte elements
 constexpr int OFF_KV = 0;                                      // stage s: K at s * 2 TILE_B, V after it
 constexpr int OFF_Q = OFF_KV + KV_STAGES * 2 * TILE_B;         // two buffers (items alternate) of two Q tiles
-constexpr int OFF_OUT = OFF_Q + 4 * TILE_B;                    // per group: output staging
-constexpr int SMEM = OFF_OUT + 2 * TILE_B + 1024;
+constexpr int SMEM = OFF_Q + 4 * TILE_B + 1024;
 constexpr int THREADS = 384;
 // barrier slots
 constexpr int B_KV_FULL = 0, B_KV_EMPTY = 4, B_Q_FULL = 8, B_Q_EMPTY = 10, B_S_READY = 12, B_P_READY = 16, B_PV_READY = 20,
@@ -49,20 +48,6 @@ __device__ __forceinline__ void ws_gather_tile(uint32_t smem_base, const uint16_
       const uint16_t* src = base + (int64_t)(src_row < 0 ? 0 : src_row) * row_stride + chunk * 8;
       cp_async16(dst, src, src_row >= 0 ? 16u : 0u);
     }
-  }
-}
-
-// staged rows -> global rows by index, by the four warps of one softmax group (8 lanes per row)
-__device__ __forceinline__ void ws_scatter_tile(const uint8_t* smem_base, uint16_t* __restrict__ base, int64_t row_stride, int my_row, int warp,
-                                                int lane) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int rl = 4 * i + (lane >> 3);
-    const int dst_row = __shfl_sync(0xffffffffu, my_row, rl);
-    const int row = warp * 32 + rl;
-    const int chunk = lane & 7;
-    const uint4 v = *reinterpret_cast<const uint4*>(smem_base + row * 128 + ((chunk ^ (row & 7)) << 4));
-    if (dst_row >= 0) *reinterpret_cast<uint4*>(base + (int64_t)dst_row * row_stride + chunk * 8) = v;
   }
 }
 
@@ -116,7 +101,6 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
     const uint32_t lane_sel = (uint32_t)(gw * 32) << 16;
     const uint32_t t_group = tmem + g * 256;
     const float scale2 = p.scale * 1.4426950408889634f;
-    uint8_t* out_stage = smem + OFF_OUT + g * TILE_B;
     uint32_t c = 0;          // key tiles this group has processed (region = c & 1, use count = c >> 1)
     bool ok = true;
     int it = 0;
@@ -242,20 +226,22 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
         mbar_arrive(bar(B_S_FREE + g * 2 + r));
       }
       HA_T_MARK(4)
-      // ---- epilogue: normalise, staged coalesced row stores ----
+      // ---- epilogue: normalise and store ----
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const float lse = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
       const long long lse_at = ((long long)(si.b * p.H + si.h)) * p.n + si.q_row0 + qrow;
       uint16_t* obase = (uint16_t*)p.o + si.b * p.o_sb + si.h * p.o_sh + si.q_row0 * p.o_sn;
+      // each thread stores its own row: 128 contiguous bytes in eight 16-byte pieces (whole 32-byte sectors pair up in
+      // L2); far less code than staging the tile and storing it row-coalesced, and this code runs once per item
+      {
+        uint4* orow = reinterpret_cast<uint4*>(obase + (int64_t)qrow * p.o_sn);
 #pragma unroll
-      for (int e = 0; e < DV; e += 2)
-        *reinterpret_cast<uint32_t*>(out_stage + swz_off(TILE, row, e)) = pack2<T>(o_acc[e] * inv, o_acc[e + 1] * inv);
+        for (int e = 0; e < DV; e += 8)
+          orow[e >> 3] = make_uint4(pack2<T>(o_acc[e] * inv, o_acc[e + 1] * inv), pack2<T>(o_acc[e + 2] * inv, o_acc[e + 3] * inv),
+                                    pack2<T>(o_acc[e + 4] * inv, o_acc[e + 5] * inv), pack2<T>(o_acc[e + 6] * inv, o_acc[e + 7] * inv));
+      }
       HA_T_MARK(6)
-      __syncwarp();          // a warp stores the 32 rows its own lanes staged
-      ws_scatter_tile(out_stage, obase, p.o_sn, qrow, gw, lane);
-      HA_T_MARK(7)
       p.lse[lse_at] = lse;
-      __syncwarp();          // ... and has read them all before the next item's rows are staged
       HA_T_MARK(5)
     }
     HA_T_DUMP(8, (int)blockIdx.x, tid == 0)
