@@ -18,6 +18,7 @@
 // TMEM columns: S [0,128) (dQ reuses [0,D) once S is consumed), dP [128,256), dV [256,256+DV), dK [384,384+D).
 #include "attn_index.cuh"
 
+#include <mutex>
 #include <type_traits>
 
 namespace ha {
@@ -264,16 +265,46 @@ __device__ __forceinline__ int bwd_q_row(const ha_attn_params& p, const BwdItem&
   return r < p.m_q ? r : -1;
 }
 
+// One unit of a persistent CTA's work list: item `item` of segment `seg`, with the row indices its first loads need.
+struct BwdWork {
+  BwdItem me;
+  SegInfo si;
+  int seg, item;
+  int qrow0, qrow1;          // local query rows of this thread for the first two list entries
+  bool valid;
+};
+
+__device__ __forceinline__ BwdWork bwd_work(const ha_attn_params& p, long long w, long long n_work, int items_per_seg, int item_base,
+                                            int items_blk, int n_chunks, int tid, bool weighted, bool paired, bool dual) {
+  BwdWork wk;
+  wk.valid = w < n_work;
+  wk.seg = 0;
+  wk.item = 0;
+  wk.qrow0 = wk.qrow1 = -1;
+  wk.me.qt_count = 0;
+  if (wk.valid) {
+    wk.seg = (int)(w / items_per_seg);
+    wk.item = (int)(w - (long long)wk.seg * items_per_seg) + item_base;
+    wk.si = seg_info(p, wk.seg);
+    wk.me = bwd_decode(p, wk.item, wk.seg, items_blk, n_chunks, tid, weighted, paired, dual);
+    wk.qrow0 = bwd_q_row(p, wk.me, wk.seg, 0, tid);
+    wk.qrow1 = bwd_q_row(p, wk.me, wk.seg, 1, tid);
+  }
+  return wk;
+}
+
 // WT: weighted sampling (sample_logw / sample_mask given); a template flag so that the plain instantiation carries none of it
 template <typename T, int D, int DV, bool WT>
-__global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p, int items_blk, int n_chunks, int pf_dist,
-                                                          int mode_bits, int item_base) {
+__global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p, int items_blk, int n_chunks, int items_per_seg,
+                                                          long long n_work, int mode_bits, int item_base,
+                                                          unsigned int* __restrict__ work_counter) {
   using Cfg = BwdCfg<D, DV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t s_base = smem_u32(smem);
   __shared__ uint64_t mma_bar;
   __shared__ uint32_t tmem_slot;
+  __shared__ long long s_next_w;     // the work item this CTA takes next (fetched by thread 0 from the launch's counter)
 
   // 256 threads = two groups of 128.  Thread (wg, row): TMEM lane `row`; in the elementwise phase group wg handles key
   // columns [64 wg, 64 wg + 64) of that row, in the reductions the column half wg of its row.
@@ -281,84 +312,19 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   const int row = tid & 127, wg = tid >> 7, qwarp = (tid >> 5) & 3;
   const bool hyper = p.mode == HA_MODE_HYPER;
   const bool causal = p.flags & HA_FLAG_CAUSAL;
-  const int seg = blockIdx.y;
-  const int item = blockIdx.x + item_base;
-  const SegInfo si = seg_info(p, seg);
   // mode_bits: 1 = block items cover whole 256-row blocks (paired); 2 = ordered dQ: the sampled items run in an earlier
   // launch, as dual items (both sampled tiles; first tile stores its dQ rows into dq_acc, second adds), and the paired
   // block items add their single contribution and write the final dq_out rows
   const bool pair_blocks = Cfg::PIPE && (mode_bits & 1), ordered = Cfg::PIPE && (mode_bits & 2);
-
-  // ---- decode the work item: key rows of this CTA and its list of query tiles ----
-  const BwdItem me = bwd_decode(p, item, seg, items_blk, n_chunks, row, WT, pair_blocks, ordered);
-  const bool paired = Cfg::PIPE && me.paired, dual = Cfg::PIPE && me.dual;
-  const int q_len = me.q_len;
-  const int krow = me.krow, qt_first = me.qt_first, qt_count = me.qt_count, k_tile = me.k_tile;
-  if (qt_count <= 0) return;     // uniform over the CTA; nothing allocated yet
   if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
 
+  // ---- once per CTA: barrier, TMEM ----
   const uint32_t bar = smem_u32(&mma_bar);
   if (tid == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
   }
   if (tid < 32) tmem_alloc(smem_u32(&tmem_slot), 512);
-
-  const long long head0 = ((long long)(si.b * p.H + si.h)) * p.n;
-  const uint16_t* qbase = (const uint16_t*)p.q + si.b * p.q_sb + si.h * p.q_sh + si.q_row0 * p.q_sn;
-  const uint16_t* gbase = (const uint16_t*)p.d_o + si.b * p.do_sb + si.h * p.do_sh + si.q_row0 * p.do_sn;
-  const uint16_t* kbase = (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
-  const uint16_t* vbase = (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn;
-  const float* lse_base = p.lse + head0 + si.q_row0;
-  const float* delta_base = p.delta + head0 + si.q_row0;
-  float* dq_base = p.dq_acc + (head0 + si.q_row0) * D;
-
-  auto q_row = [&](int jj) -> int { return bwd_q_row(p, me, seg, jj, row); };
-  // group 0 fetches the K / Q tiles, group 1 the V / dO tiles
-  auto fetch_kv = [&]() {
-    if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_K, kbase, p.k_sn, krow, qwarp, lane);
-    else bwd_gather_tile<DV>(s_base + Cfg::OFF_V, vbase, p.v_sn, krow, qwarp, lane);
-  };
-  auto fetch_kv2 = [&]() {   // paired block item: the second key tile
-    if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_K2, kbase, p.k_sn, me.krow2, qwarp, lane);
-    else bwd_gather_tile<DV>(s_base + Cfg::OFF_V2, vbase, p.v_sn, me.krow2, qwarp, lane);
-  };
-  auto fetch_q = [&](int stage, int qr) {
-    if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_Q + stage * Cfg::Q_BYTES, qbase, p.q_sn, qr, qwarp, lane);
-    else bwd_gather_tile<DV>(s_base + Cfg::OFF_DO + stage * Cfg::DO_BYTES, gbase, p.do_sn, qr, qwarp, lane);
-  };
-
-  constexpr float LOG2E = 1.4426950408889634f;
-  const float scale2 = p.scale * LOG2E;
-
-  // ---- prologue: K, V tiles and query tile 0 ----
-  fetch_kv();
-  int qrow_cur = q_row(0);
-  fetch_q(0, qrow_cur);
-  cp_async_commit();
-  float lse_cur = qrow_cur >= 0 ? lse_base[qrow_cur] * LOG2E : INFINITY;
-  float delta_cur = qrow_cur >= 0 ? delta_base[qrow_cur] : 0.f;
-  int qrow_next = q_row(1);
-
-  // ---- rows of the work item that runs pf_dist CTAs later: index loads now, L2 prefetches after the first pair ----
-  constexpr int PF_TILES = 4;
-  int pf_k = -1, pf_k2 = -1, pf_q[PF_TILES];
-#pragma unroll
-  for (int i = 0; i < PF_TILES; ++i) pf_q[i] = -1;
-  SegInfo pf_si = si;
-  {
-    const long long lin = (long long)blockIdx.y * gridDim.x + blockIdx.x + pf_dist;
-    if (hyper && pf_dist > 0 && lin < (long long)gridDim.x * gridDim.y) {
-      const int pseg = (int)(lin / gridDim.x), pitem = (int)(lin - (long long)pseg * gridDim.x) + item_base;
-      pf_si = seg_info(p, pseg);
-      const BwdItem nx = bwd_decode(p, pitem, pseg, items_blk, n_chunks, row, WT, pair_blocks, ordered);
-      if (pitem < items_blk || p.sample_idx) pf_k = nx.krow;   // default sampled rows (0..S-1) stay hot in L2 anyway
-      pf_k2 = nx.krow2;
-#pragma unroll
-      for (int i = 0; i < PF_TILES; ++i) pf_q[i] = bwd_q_row(p, nx, pseg, i, row);
-    }
-  }
-
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -373,10 +339,94 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   const uint32_t id_dq = mma_idesc(TILE, D, AB, 0, 1);
   uint8_t* sP = smem + Cfg::OFF_P;
   uint8_t* sDS = smem + Cfg::OFF_DS;
+  constexpr float LOG2E = 1.4426950408889634f;
+  const float scale2 = p.scale * LOG2E;
 
   uint32_t phase = 0;
   bool failed = false;
   HA_T_DECL(8)
+
+  // The first loads of a work item: K, V tiles and query tile 0 (one copy group), then -- pipelined schedule -- query
+  // tile 1 and a second key tile (another group).  Group 0 fetches the K / Q tiles, group 1 the V / dO tiles.  Both
+  // groups are committed even when empty, so that the waits below always count the same groups.
+  auto issue_loads = [&](const BwdWork& wk) {
+    const bool go = wk.valid && wk.me.qt_count > 0;
+    const uint16_t* qb = (const uint16_t*)p.q + wk.si.b * p.q_sb + wk.si.h * p.q_sh + wk.si.q_row0 * p.q_sn;
+    const uint16_t* gb = (const uint16_t*)p.d_o + wk.si.b * p.do_sb + wk.si.h * p.do_sh + wk.si.q_row0 * p.do_sn;
+    const uint16_t* kb = (const uint16_t*)p.k + wk.si.b * p.k_sb + wk.si.h * p.k_sh + wk.si.k_row0 * p.k_sn;
+    const uint16_t* vb = (const uint16_t*)p.v + wk.si.b * p.v_sb + wk.si.h * p.v_sh + wk.si.k_row0 * p.v_sn;
+    if (go) {
+      if (wg == 0) {
+        bwd_gather_tile<D>(s_base + Cfg::OFF_K, kb, p.k_sn, wk.me.krow, qwarp, lane);
+        bwd_gather_tile<D>(s_base + Cfg::OFF_Q, qb, p.q_sn, wk.qrow0, qwarp, lane);
+      } else {
+        bwd_gather_tile<DV>(s_base + Cfg::OFF_V, vb, p.v_sn, wk.me.krow, qwarp, lane);
+        bwd_gather_tile<DV>(s_base + Cfg::OFF_DO, gb, p.do_sn, wk.qrow0, qwarp, lane);
+      }
+    }
+    cp_async_commit();
+    if (Cfg::PIPE) {
+      if (go && wk.me.qt_count > 1) {
+        if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_Q + Cfg::Q_BYTES, qb, p.q_sn, wk.qrow1, qwarp, lane);
+        else bwd_gather_tile<DV>(s_base + Cfg::OFF_DO + Cfg::DO_BYTES, gb, p.do_sn, wk.qrow1, qwarp, lane);
+      }
+      if (go && (wk.me.paired || wk.me.dual)) {
+        if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_K2, kb, p.k_sn, wk.me.krow2, qwarp, lane);
+        else bwd_gather_tile<DV>(s_base + Cfg::OFF_V2, vb, p.v_sn, wk.me.krow2, qwarp, lane);
+      }
+      cp_async_commit();
+    }
+  };
+  auto next_work = [&](long long w) { return bwd_work(p, w, n_work, items_per_seg, item_base, items_blk, n_chunks, row, WT, pair_blocks, ordered); };
+
+  // ---- persistent loop over work items.  A CTA starts with item blockIdx.x and draws every further one from the
+  //      launch's counter (items differ in length: 1 to 16 pairs), early in the current item; the next item's first
+  //      loads are issued as soon as the last MMAs of the current one have completed, i.e. underneath its drains ----
+  auto draw_next = [&]() {
+    if (tid == 0) s_next_w = (long long)gridDim.x + atomicAdd(work_counter, 1u);
+  };
+  BwdWork cur = next_work(blockIdx.x);
+  issue_loads(cur);
+  for (long long w = blockIdx.x; w < n_work && !failed;) {
+  BwdWork nxt;
+  nxt.valid = false;
+  nxt.me.qt_count = 0;
+  const BwdItem me = cur.me;
+  const int seg = cur.seg, item = cur.item;
+  const SegInfo si = cur.si;
+  const bool paired = Cfg::PIPE && me.paired, dual = Cfg::PIPE && me.dual;
+  const int q_len = me.q_len;
+  const int krow = me.krow, qt_first = me.qt_first, qt_count = me.qt_count, k_tile = me.k_tile;
+  if (qt_count <= 0) {           // nothing to do for this item (uniform over the CTA): its (empty) copy groups retire
+    cp_async_wait<0>();
+    draw_next();
+    __syncthreads();
+    w = s_next_w;
+    __syncthreads();             // everybody has read the slot before it is written again
+    nxt = next_work(w);
+    issue_loads(nxt);
+    cur = nxt;
+    continue;
+  }
+
+  const long long head0 = ((long long)(si.b * p.H + si.h)) * p.n;
+  const uint16_t* qbase = (const uint16_t*)p.q + si.b * p.q_sb + si.h * p.q_sh + si.q_row0 * p.q_sn;
+  const uint16_t* gbase = (const uint16_t*)p.d_o + si.b * p.do_sb + si.h * p.do_sh + si.q_row0 * p.do_sn;
+  const float* lse_base = p.lse + head0 + si.q_row0;
+  const float* delta_base = p.delta + head0 + si.q_row0;
+  float* dq_base = p.dq_acc + (head0 + si.q_row0) * D;
+
+  auto q_row = [&](int jj) -> int { return bwd_q_row(p, me, seg, jj, row); };
+  auto fetch_q = [&](int stage, int qr) {
+    if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_Q + stage * Cfg::Q_BYTES, qbase, p.q_sn, qr, qwarp, lane);
+    else bwd_gather_tile<DV>(s_base + Cfg::OFF_DO + stage * Cfg::DO_BYTES, gbase, p.do_sn, qr, qwarp, lane);
+  };
+
+  // ---- K, V and query tile 0 (and tile 1 / the second key tile) are in flight already ----
+  int qrow_cur = cur.qrow0;
+  float lse_cur = qrow_cur >= 0 ? lse_base[qrow_cur] * LOG2E : INFINITY;
+  float delta_cur = qrow_cur >= 0 ? delta_base[qrow_cur] : 0.f;
+  int qrow_next = cur.qrow1;
 
   // S = Q K^T and dP = dO V^T of the query tile in stage `stg`
   auto issue_mma1 = [&](int stg, bool second = false) {
@@ -464,32 +514,6 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       }
     }
   };
-  auto prefetch_next_item = [&]() {
-    if (wg != 0) return;
-    const uint16_t* pq = (const uint16_t*)p.q + pf_si.b * p.q_sb + pf_si.h * p.q_sh + pf_si.q_row0 * p.q_sn;
-    const uint16_t* pg = (const uint16_t*)p.d_o + pf_si.b * p.do_sb + pf_si.h * p.do_sh + pf_si.q_row0 * p.do_sn;
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int kr = t == 0 ? pf_k : pf_k2;
-      if (kr >= 0) {
-        const uint16_t* pk = (const uint16_t*)p.k + pf_si.b * p.k_sb + pf_si.h * p.k_sh + (pf_si.k_row0 + kr) * p.k_sn;
-        const uint16_t* pv = (const uint16_t*)p.v + pf_si.b * p.v_sb + pf_si.h * p.v_sh + (pf_si.k_row0 + kr) * p.v_sn;
-        prefetch_l2(pk);
-        if (D > 64) prefetch_l2(pk + 64);
-        prefetch_l2(pv);
-        if (DV > 64) prefetch_l2(pv + 64);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < PF_TILES; ++i) {
-      if (pf_q[i] >= 0) {
-        prefetch_l2(pq + (int64_t)pf_q[i] * p.q_sn);
-        if (D > 64) prefetch_l2(pq + (int64_t)pf_q[i] * p.q_sn + 64);
-        prefetch_l2(pg + (int64_t)pf_q[i] * p.do_sn);
-        if (DV > 64) prefetch_l2(pg + (int64_t)pf_q[i] * p.do_sn + 64);
-      }
-    }
-  };
   const bool diag_possible = !hyper && causal;
   // dK / dV rows of a key tile (lanes = keys), one column half per thread group: fp32 reductions into the accumulators
   // (staging rows are private per warp), or -- direct mode -- stored once in the tensors' dtype (block items, which hold
@@ -541,11 +565,6 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       else
         reduce_rows<D / 2>(stg, t_src, dst, D, qrow_of_pair, row);
     };
-    if (qt_count > 1) {                       // query tile 1 goes into stage 1 right away
-      fetch_q(1, qrow_next);
-    }
-    if (paired || dual) fetch_kv2();          // the second key tile, needed from pair 2 (q_len) on
-    cp_async_commit();
     float lse_next = INFINITY, delta_next = 0.f;
     if (qt_count > 1 && qrow_next >= 0) { lse_next = lse_base[qrow_next] * LOG2E; delta_next = delta_base[qrow_next]; }
     cp_async_wait<1>();                       // K, V, query tile 0
@@ -557,6 +576,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       issue_mma1(0);
       mma_commit(bar);
     }
+    draw_next();                              // read after the pair loop's barriers, below
     int qrow_prev = -1;
     for (int jj = 0; jj < qt_count; ++jj) {
       HA_T_MARK(0)
@@ -603,7 +623,6 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       // underneath the batch: dQ of the previous pair (paired item: of query tile 0, complete after pair 2)
       if (jj >= 1 && (!paired || jj == 3)) drain_dq(jj - 1, qrow_prev);
       HA_T_MARK(5)
-      if (jj == 0) prefetch_next_item();
       if (jj == 0 && ordered && paired && p.sample_size > 0) {
         // the sampled launch's partial dQ rows of both query tiles: into L2 now, read by the final drains
         if (qrow_cur >= 0) prefetch_l2(dq_base + (int64_t)qrow_cur * D + wg * (D / 2));
@@ -621,13 +640,17 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     }
     cp_async_wait<0>();
     if (!failed) {
+      nxt = next_work(s_next_w);                     // its index loads travel while the last batch runs
       if (!mbar_wait(bar, phase)) failed = true;     // last batch
       phase ^= 1;
       tc_fence_after();
       failed = __syncthreads_or(failed);
     }
     HA_T_MARK(6)
-    if (!failed) drain_dq(qt_count - 1, qrow_prev);
+    if (!failed) {
+      issue_loads(nxt);                              // every operand tile is free now
+      drain_dq(qt_count - 1, qrow_prev);
+    }
   } else {
     // ------------------------------------------------------------------------------------------------------------
     // Serial schedule (head dim 128: TMEM has no room for a separate dQ buffer, shared memory none for a second stage)
@@ -645,6 +668,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
         issue_mma1(0);
         mma_commit(bar);
       }
+      if (jj == 0) draw_next();               // read after this loop (every iteration has barriers)
       if (!mbar_wait(bar, phase)) failed = true;
       phase ^= 1;
       tc_fence_after();
@@ -680,10 +704,13 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       qrow_next = qrow_after;
       lse_cur = lse_next;
       delta_cur = delta_next;
-      if (jj == 0) prefetch_next_item();
     }
     cp_async_wait<0>();
     HA_T_MARK(6)
+    if (!failed) {
+      nxt = next_work(s_next_w);
+      issue_loads(nxt);                              // every MMA of this item has completed: the operand tiles are free
+    }
   }
 
   if (failed) {
@@ -693,10 +720,32 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     drain_kv((paired || dual) ? me.krow2 : krow, dual ? 1 : k_tile);
   }
   HA_T_MARK(7)
-  HA_T_DUMP(8, (int)(blockIdx.y * gridDim.x + blockIdx.x), tid == 0)
+  w = failed ? n_work : s_next_w;    // (the slot is rewritten only after the next item's first barrier)
+  cur = nxt;
+  }   // work items
+  cp_async_wait<0>();
+  HA_T_DUMP(8, (int)blockIdx.x, tid == 0)
   tc_fence_before();
   __syncthreads();
   if (tid < 32) tmem_dealloc(tmem, 512);
+}
+
+// Work counters of the persistent launches: 256 words in the library image per device; a launch takes the next one in
+// rotation (so launches in flight on different streams do not share a word) and zeroes it on its stream first.
+static __device__ unsigned int g_work_counters[256];
+static unsigned int* next_work_counter() {
+  static std::mutex mu;
+  static unsigned int* base[64] = {nullptr};
+  static unsigned int turn[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_work_counters) != cudaSuccess) return nullptr;
+    base[dev] = (unsigned int*)ptr;
+  }
+  return base[dev] + (turn[dev]++ % 256u);
 }
 
 template <typename T, int D, int DV, bool WT>
@@ -727,16 +776,27 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int pf_dist = p.mode == HA_MODE_HYPER ? sms : 0;   // one CTA per SM is resident: the next wave is `sms` items away
+  // persistent CTAs, one per SM (512 TMEM columns, > 190 KB shared memory each): CTA c starts with work item c and
+  // draws the following ones from a counter, which is one of a small rotating set of device words zeroed in stream
+  // order before the launch
+  auto launch = [&](long long items_per_seg, int mode_bits, int item_base) -> int {
+    const long long n_work = items_per_seg * segs;
+    const unsigned grid = (unsigned)(n_work < sms ? n_work : sms);
+    unsigned int* ctr = next_work_counter();
+    if (!ctr) return HA_ERR_CUDA;
+    HA_CUDA_OK(cudaMemsetAsync(ctr, 0, sizeof(unsigned int), st), "ha_attn_bwd work counter");
+    attn_tc_bwd_kernel<T, D, DV, WT><<<grid, 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, (int)items_per_seg, n_work, mode_bits, item_base, ctr);
+    return HA_OK;
+  };
+  int lrc;
   if (ordered) {
     if (p.sample_size > 0) {
-      attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)n_chunks_dual, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist, 3,
-                                                                                                           items_blk);
+      if ((lrc = launch(n_chunks_dual, 3, items_blk)) != HA_OK) return lrc;
       HA_LAUNCHED("ha_attn_bwd (tcgen05, sampled items)");
     }
-    attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)items_blk, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist, 3, 0);
+    if ((lrc = launch(items_blk, 3, 0)) != HA_OK) return lrc;
   } else {
-    attn_tc_bwd_kernel<T, D, DV, WT><<<dim3((unsigned)items, (unsigned)segs), 256, Cfg::SMEM, st>>>(p, items_blk, n_chunks, pf_dist, pair_blocks, 0);
+    if ((lrc = launch(items, pair_blocks, 0)) != HA_OK) return lrc;
   }
   HA_LAUNCHED("ha_attn_bwd (tcgen05)");
   return HA_OK;
