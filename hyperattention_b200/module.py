@@ -78,7 +78,7 @@ class HyperAttention(torch.nn.Module):
         self.fused_causal = kwargs.get('fused_causal', True)
         self.kernel_flags = kwargs.get('kernel_flags', 0)
         # 'reference': sampled part = key rows 0..sample_size-1, unweighted (what the reference's kernels compute).
-        # 'uniform':   sample_size distinct key rows drawn uniformly per (batch, head), the query tile's own block
+        # 'uniform':   sample_size distinct key rows per (batch, head), one uniform draw per stratum, the query tile's own block
         #              excluded, importance-weighted to stand for all keys outside the block (no reference counterpart).
         self.sampling = kwargs.get('sampling', 'reference')
         self.sample_generator = kwargs.get('sample_generator')   # torch.Generator on the inputs' device, or None
@@ -184,9 +184,13 @@ class HyperAttention(torch.nn.Module):
             q_idx, k_idx = idx[:B * H].view(B, H, n_query), idx[B * H:].view(B, H, n_query)
             sample_idx, weighted = None, False
             if self.sampling == 'uniform' and self.sample_size > 0:
-                # distinct uniform rows per (batch, head): the positions of the largest of n uniform variates
-                u = torch.rand(B * H, key.shape[2], device=key.device, generator=self.sample_generator)
-                sample_idx = u.topk(self.sample_size, dim=-1).indices.to(torch.int32)
+                # distinct rows with equal inclusion probability per (batch, head): one uniform draw from each of
+                # sample_size equal strata of the key range (cheaper than a draw without replacement, lower variance)
+                n_k, S = key.shape[2], self.sample_size
+                edges = (torch.arange(S + 1, device=key.device, dtype=torch.int64) * n_k) // S
+                u = torch.rand(B * H, S, device=key.device, generator=self.sample_generator)
+                size = edges[1:] - edges[:-1]
+                sample_idx = (edges[:-1] + torch.minimum((u * size).long(), size - 1)).to(torch.int32)
                 self.last_sample_idx = sample_idx.view(B, H, self.sample_size)
                 weighted = True
             attn, lse = ops.hyper_attn_func(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2),
