@@ -279,9 +279,9 @@ def main():
 
 # DRAM traffic of the dominant kernel (attn_tc_bwd_kernel, hyper pattern: its two launches per backward, sampled items then
 # block items), from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of the 8-head x 65536-token case, which
-# scales linearly with the number of rows (fixed work per row): 196.7 + 411.3 MB read, 95.6 + 164.1 MB written for
+# scales linearly with the number of rows (fixed work per row): 159.1 + 411.3 MB read, 92.7 + 160.3 MB written for
 # 524288 rows.  Summary of the capture: profiles/attn_tc_bwd_kernel_hyper_8x65536.md.
-BWD_DRAM_BYTES_PER_ROW = 1655.0
+BWD_DRAM_BYTES_PER_ROW = 1570.0
 
 
 def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
