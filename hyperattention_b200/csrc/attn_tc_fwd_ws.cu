@@ -139,14 +139,6 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
         if (!(ok = wait(B_S_READY + g * 2 + r, (c >> 1) & 1))) break;
         tc_fence_after();
         HA_T_MARK(1)
-        if (j >= 1) {
-          // the product of the previous tile (other region): fold it, then hand the region back for S of tile j+1
-          if (!(ok = wait(B_PV_READY + g * 2 + (r ^ 1), ((c - 1) >> 1) & 1))) break;
-          tc_fence_after();
-          fold_pv(t_group + (r ^ 1) * 128 + 64, alpha_prev);
-          tc_fence_before();
-          mbar_arrive(bar(B_S_FREE + g * 2 + (r ^ 1)));
-        }
         HA_T_MARK(2)
         // ---- softmax over this tile's 128 columns (every column is visible in this pattern) ----
         float mx;
@@ -170,6 +162,16 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
             if (cc + 1 < 4) tmem_ld_fence(nxt);
           }
           mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        }
+        if (j >= 1) {
+          // The product of the previous tile (other region), folded here rather than before the max pass: its MMAs were
+          // issued when this group finished that tile's P and have had the max pass to complete.  Then the region goes
+          // back for S of tile j+1.
+          if (!(ok = wait(B_PV_READY + g * 2 + (r ^ 1), ((c - 1) >> 1) & 1))) break;
+          tc_fence_after();
+          fold_pv(t_group + (r ^ 1) * 128 + 64, alpha_prev);
+          tc_fence_before();
+          mbar_arrive(bar(B_S_FREE + g * 2 + (r ^ 1)));
         }
         const float m_new = fmaxf(m_run, mx * scale2);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
