@@ -6,7 +6,8 @@
 //   * group 0 / group 1 (128 threads each): softmax and output of query tile 2b / 2b+1; thread i owns query row i =
 //     TMEM lane i, as in the one-tile kernel (attn_tc_fwd.cu), whose arithmetic this file repeats step for step.
 //   * loader warp: gathers rows by index with 16-byte cp.async into a ring of four K/V stages (each key tile is fetched
-//     once for both query tiles) and the two Q tiles (double buffered over the items); it runs ahead of the compute
+//     once for both query tiles), the two Q tiles (double buffered over the items) and, for a merging call, the rows
+//     already stored for the two query tiles; it runs ahead of the compute
 //     across items, so index -> row latency and the next item's prologue are off the critical path.
 //   * MMA warp (one thread): issues S = Q K^T for both groups one key tile ahead of their softmax, and P V as soon as
 //     a group has written P; every completion is a tcgen05.commit onto an mbarrier.
@@ -26,11 +27,12 @@ constexpr int KV_STAGES = 4;
 constexpr int TILE_B = TILE * 64 * 2;                          // one 128 x 64 tile of 2-byte elements
 constexpr int OFF_KV = 0;                                      // stage s: K at s * 2 TILE_B, V after it
 constexpr int OFF_Q = OFF_KV + KV_STAGES * 2 * TILE_B;         // two buffers (items alternate) of two Q tiles
-constexpr int SMEM = OFF_Q + 4 * TILE_B + 1024;
+constexpr int OFF_OLD = OFF_Q + 4 * TILE_B;                    // per group: the previously stored o rows of its tile (merge)
+constexpr int SMEM = OFF_OLD + 2 * TILE_B + 1024;
 constexpr int THREADS = 384;
 // barrier slots
 constexpr int B_KV_FULL = 0, B_KV_EMPTY = 4, B_Q_FULL = 8, B_Q_EMPTY = 10, B_S_READY = 12, B_P_READY = 16, B_PV_READY = 20,
-              B_S_FREE = 24, N_BARS = 28;
+              B_S_FREE = 24, B_OLD_FULL = 28, B_OLD_EMPTY = 30, N_BARS = 32;
 }  // namespace ws
 
 // 128 rows x 64 elements gathered by ONE warp: rows[q] = source row of tile row 32 q + lane (-1: zero fill)
@@ -62,6 +64,7 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool merge = p.flags & HA_FLAG_MERGE;
   const int n_blk = 2;                                   // window tiles of a block (block size rounded up to 256)
   const int n_tiles = n_blk + p.sample_size / TILE;      // key tiles per item
 
@@ -71,8 +74,9 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
     // arrivals per phase: 32 (every loader lane, when its copies have landed) on the "full" barriers, 128 (a softmax
     // group) on P-ready / S-free, 1 (a tcgen05.commit or one elected thread) elsewhere
     for (int i = 0; i < N_BARS; ++i) {
-      const bool by_loader = (i >= B_KV_FULL && i < B_KV_FULL + KV_STAGES) || (i >= B_Q_FULL && i < B_Q_FULL + 2);
-      const bool by_group = (i >= B_P_READY && i < B_PV_READY) || i >= B_S_FREE;
+      const bool by_loader = (i >= B_KV_FULL && i < B_KV_FULL + KV_STAGES) || (i >= B_Q_FULL && i < B_Q_FULL + 2) ||
+                             (i >= B_OLD_FULL && i < B_OLD_FULL + 2);
+      const bool by_group = (i >= B_P_READY && i < B_PV_READY) || (i >= B_S_FREE && i < B_S_FREE + 4) || i >= B_OLD_EMPTY;
       mbar_init(bar(i), by_loader ? 32 : by_group ? 128 : 1);
     }
     s_abort = 0;
@@ -116,6 +120,8 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
       const SegInfo si = seg_info(p, seg);
       const int qrow = qrow_next;
       qrow_next = item_qrow(item + gridDim.x);     // the next item's row index arrives while this item computes
+      const long long lse_at = ((long long)(si.b * p.H + si.h)) * p.n + si.q_row0 + qrow;
+      const float lse_old = merge ? p.lse[lse_at] : 0.f;       // (merge) needed in the epilogue: requested now
       __align__(8) float o_acc[DV];
 #pragma unroll
       for (int i = 0; i < DV; ++i) o_acc[i] = 0.f;
@@ -228,19 +234,62 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
         mbar_arrive(bar(B_S_FREE + g * 2 + r));
       }
       HA_T_MARK(4)
-      // ---- epilogue: normalise and store ----
+      // ---- epilogue: normalise, optionally merge with the stored (o, lse), store ----
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      const float lse = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
-      const long long lse_at = ((long long)(si.b * p.H + si.h)) * p.n + si.q_row0 + qrow;
+      const float lse_own = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      float lse = lse_own;
       uint16_t* obase = (uint16_t*)p.o + si.b * p.o_sb + si.h * p.o_sh + si.q_row0 * p.o_sn;
-      // each thread stores its own row: 128 contiguous bytes in eight 16-byte pieces (whole 32-byte sectors pair up in
-      // L2); far less code than staging the tile and storing it row-coalesced, and this code runs once per item
-      {
-        uint4* orow = reinterpret_cast<uint4*>(obase + (int64_t)qrow * p.o_sn);
+      float w1 = 0.f, w2 = 1.f;
+      if (merge) {
+        const float l1 = lse_old, l2 = lse_own;
+        if (p.flags & HA_FLAG_MERGE_EXACT) {
+          const float m2 = fmaxf(l1, l2);
+          const float e1 = __expf(l1 - m2), e2 = __expf(l2 - m2);
+          w1 = e1 / (e1 + e2);
+          w2 = e2 / (e1 + e2);
+          lse = m2 + __logf(e1 + e2);
+        } else {
+          const float cf = round_to<T>(1.f / (1.f + __expf(l2 - l1)));
+          w1 = cf;
+          w2 = round_to<T>(1.f - cf);
+          lse = l1 - __logf(cf + 1.1920929e-07f);
+        }
+      }
+      // Each thread stores its own row: 128 contiguous bytes in eight 16-byte pieces (whole 32-byte sectors pair up in
+      // L2); far less code than staging the tile and storing it row-coalesced, and this code runs once per item.
+      if (p.part_o) {      // the un-merged result of this call
+        uint4* prow = reinterpret_cast<uint4*>((uint16_t*)p.part_o + si.b * p.o_sb + si.h * p.o_sh + (si.q_row0 + qrow) * p.o_sn);
 #pragma unroll
         for (int e = 0; e < DV; e += 8)
-          orow[e >> 3] = make_uint4(pack2<T>(o_acc[e] * inv, o_acc[e + 1] * inv), pack2<T>(o_acc[e + 2] * inv, o_acc[e + 3] * inv),
+          prow[e >> 3] = make_uint4(pack2<T>(o_acc[e] * inv, o_acc[e + 1] * inv), pack2<T>(o_acc[e + 2] * inv, o_acc[e + 3] * inv),
                                     pack2<T>(o_acc[e + 4] * inv, o_acc[e + 5] * inv), pack2<T>(o_acc[e + 6] * inv, o_acc[e + 7] * inv));
+        if (p.part_lse) p.part_lse[lse_at] = lse_own;
+      }
+      {
+        uint4* orow = reinterpret_cast<uint4*>(obase + (int64_t)qrow * p.o_sn);
+        if (merge) {
+          // the rows stored before this call were fetched by the loader; chunk c of row r sits at chunk c ^ (r & 7)
+          if (!(ok = wait(B_OLD_FULL + g, it & 1))) break;
+          const uint8_t* old_row = smem + OFF_OLD + g * TILE_B + row * 128;
+#pragma unroll
+          for (int e = 0; e < DV; e += 8) {
+            const uint4 ov = *reinterpret_cast<const uint4*>(old_row + ((((e >> 3) ^ (row & 7))) << 4));
+            const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w};
+            uint32_t w[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const float2 old = unpack2<T>(ow[h]);
+              w[h] = pack2<T>(w1 * old.x + w2 * round_to<T>(o_acc[e + 2 * h] * inv), w1 * old.y + w2 * round_to<T>(o_acc[e + 2 * h + 1] * inv));
+            }
+            orow[e >> 3] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          mbar_arrive(bar(B_OLD_EMPTY + g));       // this thread has read its row: the loader may refill the tile
+        } else {
+#pragma unroll
+          for (int e = 0; e < DV; e += 8)
+            orow[e >> 3] = make_uint4(pack2<T>(o_acc[e] * inv, o_acc[e + 1] * inv), pack2<T>(o_acc[e + 2] * inv, o_acc[e + 3] * inv),
+                                      pack2<T>(o_acc[e + 4] * inv, o_acc[e + 5] * inv), pack2<T>(o_acc[e + 6] * inv, o_acc[e + 7] * inv));
+        }
       }
       HA_T_MARK(6)
       p.lse[lse_at] = lse;
@@ -302,6 +351,17 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
           push(B_KV_FULL + stage);
 #pragma unroll
           for (int q = 0; q < 4; ++q) krows[q] = knext[q];
+        }
+        // (merge) the rows stored before this call, needed in the item's epilogue only: fetched last, so that waiting
+        // for the previous item's epilogue to release the buffer does not hold up this item's key tiles
+        if (merge && ok) {
+          const uint16_t* obase = (const uint16_t*)p.o + si.b * p.o_sb + si.h * p.o_sh + si.q_row0 * p.o_sn;
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            if (it > 0 && !(ok = wait(B_OLD_EMPTY + x, (it - 1) & 1))) break;
+            ws_gather_tile(s_base + OFF_OLD + x * TILE_B, obase, p.o_sn, qrows[x], lane);
+            push(B_OLD_FULL + x);
+          }
         }
       }
       cp_async_commit();
@@ -406,9 +466,7 @@ bool ws_fwd_supported(const ha_attn_params& p) {
   if (p.mode != HA_MODE_HYPER || p.d != 64 || p.dv != 64) return false;
   if (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_NO_WS)) return false;
   if (p.sample_logw) return false;                                   // weighted sampling stays on the one-tile kernel
-  // The in-place merge of the causal schedule (and its un-merged part outputs) stays on the one-tile kernel: with the
-  // merge's extra row traffic handled serially by the softmax groups this design measured 9.6 ms against 8.95 ms there.
-  if ((p.flags & HA_FLAG_MERGE) || p.part_o) return false;
+  if (p.part_o && (uintptr_t)p.part_o % 16 != 0) return false;
   if ((p.block_size + TILE - 1) / TILE != 2 || p.m_q % (2 * TILE) != 0 || p.m_q != p.m_k) return false;
   return true;
 }

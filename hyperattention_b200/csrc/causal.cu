@@ -236,7 +236,7 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
   for (int l = p.levels - 1; l >= 0; --l) {
     const int span = p.n >> l, m = span / 2;
     a.mode = HA_MODE_HYPER;
-    a.flags = HA_FLAG_MERGE | (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_MERGE_EXACT | HA_FLAG_FORCE_SIMT));
+    a.flags = HA_FLAG_MERGE | (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_MERGE_EXACT | HA_FLAG_FORCE_SIMT | HA_FLAG_NO_WS));
     a.segs_per_head = 1 << l;
     a.span = span; a.q_off = m; a.k_off = 0; a.m_q = m; a.m_k = m;
     a.q_idx = sv.q_idx(l); a.k_idx = sv.k_idx(l); a.sample_idx = nullptr;

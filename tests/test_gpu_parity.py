@@ -497,3 +497,25 @@ def test_persistent_forward_matches_one_tile_forward(ha, cfg):
     o1, l1 = ha.hyper_attn_func(*args, 0)
     o2, l2 = ha.hyper_attn_func(*args, L.FLAG_NO_WS)
     assert torch.equal(o1, o2) and torch.equal(l1, l2)
+
+
+def test_persistent_forward_in_the_causal_schedule_matches_one_tile_forward(ha):
+    """the merging rectangle launches of the causal schedule through the persistent forward (default) and through the
+    one-tile kernel (HA_FLAG_NO_WS): identical outputs, lse and -- reference gradient convention, which reads the
+    un-merged part outputs -- gradients up to the order of fp32 atomic additions"""
+    import hyperattention_b200 as hb
+    from hyperattention_b200 import _lib as L
+    torch.manual_seed(51)
+    B, H, n, d = 1, 3, 4096, 64
+    q, k, v, do = [torch.randn(B, H, n, d).bfloat16() for _ in range(4)]
+    outs = []
+    for flags in (0, L.FLAG_NO_WS):
+        mod = hb.HyperAttention(input_dim=d, block_size=256, sample_size=256, min_seq_len=512, kernel_flags=flags,
+                                rng=torch.Generator().manual_seed(2)).cuda().to(dtype=torch.bfloat16)
+        qg, kg, vg = [dev(t).requires_grad_() for t in (q, k, v)]
+        o, lse = mod(qg, kg, vg, causal=True, return_lse=True)
+        o.backward(dev(do))
+        outs.append((o.detach(), lse.detach(), qg.grad, kg.grad, vg.grad))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    for a, b in zip(outs[0][2:], outs[1][2:]):
+        assert rel(a, b) < 2e-3
