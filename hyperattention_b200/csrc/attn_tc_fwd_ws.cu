@@ -53,7 +53,9 @@ __device__ __forceinline__ void ws_gather_tile(uint32_t smem_base, const uint16_
   }
 }
 
-template <typename T>
+// MG: merging call (HA_FLAG_MERGE; may also write the un-merged rows); a template flag so that the plain instantiation
+// carries none of it
+template <typename T, bool MG>
 __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha_attn_params p, const int n_items, const int blocks_per_seg) {
   using namespace ws;
   extern __shared__ uint8_t smem_raw[];
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool merge = p.flags & HA_FLAG_MERGE;
+  constexpr bool merge = MG;
   const int n_blk = 2;                                   // window tiles of a block (block size rounded up to 256)
   const int n_tiles = n_blk + p.sample_size / TILE;      // key tiles per item
 
@@ -100,6 +102,9 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
     // =====================================================================================================
     // softmax groups
     // =====================================================================================================
+    // Register budget: 384 threads x 168 at launch.  The loader / MMA warpgroup gives registers back (56 each), the two
+    // softmax groups take 224 each: 2 x 128 x 224 + 128 x 56 = 64512 of the SM's 65536, i.e. with slack -- a request that
+    // the pool cannot satisfy would wait forever.
     asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int g = warp >> 2, gw = warp & 3, row = tid & 127;
     const uint32_t lane_sel = (uint32_t)(gw * 32) << 16;
@@ -257,7 +262,7 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
       }
       // Each thread stores its own row: 128 contiguous bytes in eight 16-byte pieces (whole 32-byte sectors pair up in
       // L2); far less code than staging the tile and storing it row-coalesced, and this code runs once per item.
-      if (p.part_o) {      // the un-merged result of this call
+      if (MG && p.part_o) {      // the un-merged result of this call
         uint4* prow = reinterpret_cast<uint4*>((uint16_t*)p.part_o + si.b * p.o_sb + si.h * p.o_sh + (si.q_row0 + qrow) * p.o_sn);
 #pragma unroll
         for (int e = 0; e < DV; e += 8)
@@ -466,7 +471,7 @@ bool ws_fwd_supported(const ha_attn_params& p) {
   if (p.mode != HA_MODE_HYPER || p.d != 64 || p.dv != 64) return false;
   if (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_NO_WS)) return false;
   if (p.sample_logw) return false;                                   // weighted sampling stays on the one-tile kernel
-  if (p.part_o && (uintptr_t)p.part_o % 16 != 0) return false;
+  if (p.part_o && (!(p.flags & HA_FLAG_MERGE) || (uintptr_t)p.part_o % 16 != 0)) return false;
   if ((p.block_size + TILE - 1) / TILE != 2 || p.m_q % (2 * TILE) != 0 || p.m_q != p.m_k) return false;
   return true;
 }
@@ -481,15 +486,21 @@ int ws_attn_fwd(const ha_attn_params& p, cudaStream_t st) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = (int)(items < sms ? items : sms);
+  const bool mg = p.flags & HA_FLAG_MERGE;
+#define HA_WS_LAUNCH(TT, MM)                                                                                                     \
+  do {                                                                                                                           \
+    HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_fwd_ws_kernel<TT, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, ws::SMEM),        \
+               "ha_attn_fwd smem attribute");                                                                                    \
+    attn_tc_fwd_ws_kernel<TT, MM><<<grid, ws::THREADS, ws::SMEM, st>>>(p, (int)items, blocks_per_seg);                           \
+  } while (0)
   if (p.dtype == HA_BF16) {
-    HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_fwd_ws_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, ws::SMEM),
-               "ha_attn_fwd smem attribute");
-    attn_tc_fwd_ws_kernel<__nv_bfloat16><<<grid, ws::THREADS, ws::SMEM, st>>>(p, (int)items, blocks_per_seg);
+    if (mg) HA_WS_LAUNCH(__nv_bfloat16, true);
+    else HA_WS_LAUNCH(__nv_bfloat16, false);
   } else {
-    HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_fwd_ws_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, ws::SMEM),
-               "ha_attn_fwd smem attribute");
-    attn_tc_fwd_ws_kernel<__half><<<grid, ws::THREADS, ws::SMEM, st>>>(p, (int)items, blocks_per_seg);
+    if (mg) HA_WS_LAUNCH(__half, true);
+    else HA_WS_LAUNCH(__half, false);
   }
+#undef HA_WS_LAUNCH
   HA_LAUNCHED("ha_attn_fwd (tcgen05, warp-specialised)");
   return HA_OK;
 }
