@@ -1,7 +1,10 @@
 // Attention backward on tcgen05 tensor cores + TMEM, bf16/fp16, head dims 64 and 128.
 //
-// One CTA of 256 threads (two groups of 128; thread (g, i) = TMEM lane i, the groups split the columns of the
-// elementwise phase and of the reductions) owns one tile of 128 keys and walks the query tiles that pair with it.
+// Persistent CTAs of 256 threads (two groups of 128; thread (g, i) = TMEM lane i, the groups split the columns of the
+// elementwise phase and of the reductions), one per SM.  A CTA works through work items: it starts with item blockIdx.x
+// and draws every further one from the launch's counter; a work item owns one tile of 128 keys (or the two key tiles of
+// a 256-row block, or both sampled tiles) and walks the query tiles that pair with it.  As soon as an item's last MMAs
+// have completed, the next item's K / V / Q / dO gathers are issued, so they travel while its gradient rows drain.
 // Per (key tile, query tile) pair:
 //   S  = Q K^T    (lanes = queries)      dP = dO V^T   (lanes = queries)            -> TMEM, fp32
 //   p  = exp2(S*scale*log2e - lse*log2e),  ds = p * (dP - delta) * scale            per thread: its query row
@@ -10,12 +13,15 @@
 //   dV += P^T dO  (lanes = keys, accumulates in TMEM over the query tiles)
 //   dK += dS^T Q  (lanes = keys, accumulates in TMEM)
 //   dQ  = dS K    (lanes = queries) -> staged through shared memory -> coalesced fp32 vector reductions into dq_acc
-// At the end the key tile's dK/dV rows are reduced into dk_acc/dv_acc the same way.
+//                 (or, ordered mode, a plain store by the first contributor and the final typed rows by the last)
+// At the end of a key tile its dK/dV rows are reduced into dk_acc/dv_acc the same way, or stored once in the tensors'
+// dtype where one work item holds the complete sum (dk_out / dv_out; HA_FLAG_BWD_KV_INIT).
 //
-// Work items of a segment: hyper = one item per sorted key tile (block window of query tiles through q_idx), plus
-// (sampled key tile x chunk of query tiles in natural order) items; flash = (key tile x chunk of query tiles) with the
-// causal mask applied on the diagonal pair.
-// TMEM columns: S [0,128) (dQ reuses [0,D) once S is consumed), dP [128,256), dV [256,256+DV), dK [384,384+D).
+// Work items of a segment: hyper = one item per sorted key tile (block window of query tiles through q_idx) or per
+// 256-row block, plus (sampled key tile x chunk of query tiles) items; flash = (key tile x chunk of query tiles) with
+// the causal mask applied on the diagonal pair.
+// TMEM columns (head dims 64): S [0,128), dP [128,256), dV [256,320), dK [320,384), dQ two buffers [384,512);
+// (head dim 128): S [0,128) (dQ reuses [0,D) once S is consumed), dP [128,256), dV [256,256+DV), dK [384,384+D).
 #include "attn_index.cuh"
 
 #include <mutex>
