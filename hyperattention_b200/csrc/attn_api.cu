@@ -35,7 +35,7 @@ static int check_common(const ha_attn_params& p, bool backward) {
     return HA_ERR_INVALID;
   }
   if (backward) {
-    if (!p.d_o || !p.delta || !p.dq_acc) return HA_ERR_INVALID;
+    if (!p.d_o || !p.delta || (!p.dq_acc && !p.dq_out)) return HA_ERR_INVALID;
     if (p.dk_out || p.dv_out) {
       // direct dK/dV: hyper pattern only (one work item owns a key tile's block part), both outputs, slot buffers if sampled
       if (!p.dk_out || !p.dv_out || p.mode != HA_MODE_HYPER) return HA_ERR_INVALID;

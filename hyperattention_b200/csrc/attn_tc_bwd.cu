@@ -13,7 +13,7 @@
 //   dV += P^T dO  (lanes = keys, accumulates in TMEM over the query tiles)
 //   dK += dS^T Q  (lanes = keys, accumulates in TMEM)
 //   dQ  = dS K    (lanes = queries) -> staged through shared memory -> coalesced fp32 vector reductions into dq_acc
-//                 (or, ordered mode, a plain store by the first contributor and the final typed rows by the last)
+//                 (or, where one work item holds a query tile's complete sum, the final typed rows: dq_out)
 // At the end of a key tile its dK/dV rows are reduced into dk_acc/dv_acc the same way, or stored once in the tensors'
 // dtype where one work item holds the complete sum (dk_out / dv_out; HA_FLAG_BWD_KV_INIT).
 //
@@ -89,12 +89,12 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 // NC floats (16-byte chunk c of row r at position c ^ (r & 7) of its 128-byte group); a warp only touches the 32 rows of
 // its own lanes, so a warp-level sync suffices.  (A TMA bulk reduce-add per row was measured slower than this.)
 // MODE 0: red.add into fp32 rows.  MODE 1: plain fp32 store (first contribution to rows nobody has written yet).
-// MODE 2: last contribution: (fp32 row, if has_partial) + value -> stored in type T at `out` (same row / column layout).
+// MODE 2: the complete sum: stored in type T at `out` (same row / column layout); nothing is read.
 // Every mode maps (row, 16-byte chunk) to the same lane, so a store and a later reduction of one address come from one
 // thread, in program order.
 template <int NC, int MODE = 0, typename T = float>
 __device__ __forceinline__ void reduce_rows(uint8_t* stage, uint32_t tmem_addr, float* __restrict__ base, int64_t row_stride, int my_row,
-                                            int row, T* __restrict__ out = nullptr, bool has_partial = true) {
+                                            int row, T* __restrict__ out = nullptr) {
   const int lane = row & 31, qwarp = row >> 5;
   float* srow = reinterpret_cast<float*>(stage) + row * NC;
 #pragma unroll
@@ -115,23 +115,15 @@ __device__ __forceinline__ void reduce_rows(uint8_t* stage, uint32_t tmem_addr, 
   constexpr int NI = 32 / RPI;
   const int chunk = lane % CPR;
   if constexpr (MODE == 2) {
-    // all loads of the partial sums first (independent, one DRAM round trip), then add, convert and store
-    int dst_rows[NI];
-    float4 part[NI];
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
-      dst_rows[i] = __shfl_sync(0xffffffffu, my_row, i * RPI + lane / CPR);
-      part[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (has_partial && dst_rows[i] >= 0) part[i] = __ldcs(reinterpret_cast<const float4*>(base + (int64_t)dst_rows[i] * row_stride + chunk * 4));
-    }
-#pragma unroll
-    for (int i = 0; i < NI; ++i) {
-      const int rr = qwarp * 32 + i * RPI + lane / CPR;
+      const int rl = i * RPI + lane / CPR;
+      const int dst_row = __shfl_sync(0xffffffffu, my_row, rl);
+      const int rr = qwarp * 32 + rl;
       const int sw = (chunk & ~7) | ((chunk ^ rr) & 7);
       const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + rr * NC + sw * 4);
-      if (dst_rows[i] >= 0)
-        *reinterpret_cast<uint2*>(out + (int64_t)dst_rows[i] * row_stride + chunk * 4) =
-            make_uint2(pack2<T>(v.x + part[i].x, v.y + part[i].y), pack2<T>(v.z + part[i].z, v.w + part[i].w));
+      if (dst_row >= 0)
+        *reinterpret_cast<uint2*>(out + (int64_t)dst_row * row_stride + chunk * 4) = make_uint2(pack2<T>(v.x, v.y), pack2<T>(v.z, v.w));
     }
   } else {
 #pragma unroll
@@ -177,8 +169,8 @@ struct BwdItem {
   int krow;                  // local key row fetched / owned by thread tid (-1: none)
   int krow2;                 // paired block item: row of the second key tile
   bool paired;               // block item over BOTH key tiles of a 256-row block: pairs (A,Q0) (A,Q1) (B,Q0) (B,Q1)
-  bool dual;                 // sampled item over BOTH sampled tiles: q_len pairs with tile A, then q_len pairs with tile B
-  int q_len;                 // query tiles of the item (dual: qt_count = 2 * q_len pairs)
+  bool fused;                // paired item that also takes the two sampled key tiles: eight pairs (A, B, S0, S1) x (Q0, Q1)
+  int srow0, srow1;          // fused item: this thread's rows of the two sampled key tiles
   int qt_first, qt_count;    // natural-order query tiles [qt_first, qt_first + qt_count) ...
   bool q_sorted;             // ... or, when set, qt_count tiles of sorted positions starting at q_pos0 (modulo m_q)
   int q_pos0;
@@ -186,12 +178,12 @@ struct BwdItem {
 };
 
 __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item, int seg, int items_blk, int n_chunks, int tid,
-                                              bool weighted, bool paired, bool dual) {
+                                              bool weighted, bool paired, bool fused) {
   BwdItem it;
+  it.fused = false;
+  it.srow0 = it.srow1 = -1;
   it.krow2 = -1;
   it.paired = false;
-  it.dual = false;
-  it.q_len = 0;
   const bool hyper = p.mode == HA_MODE_HYPER;
   const int n_qt = (p.m_q + TILE - 1) / TILE;
   it.krow = -1;
@@ -208,6 +200,13 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
     it.q_sorted = true;
     it.q_pos0 = it.k_tile * TILE;
     it.qt_count = 4;
+    if (fused) {
+      // ... and the two sampled key tiles against the same two query tiles: pairs 4..7
+      it.fused = true;
+      it.qt_count = 8;
+      it.srow0 = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + tid] : tid;
+      it.srow1 = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + TILE + tid] : TILE + tid;
+    }
   } else if (hyper && item < items_blk) {
     it.k_tile = item;
     it.krow = p.k_idx[(long long)seg * p.m_k + it.k_tile * TILE + tid];
@@ -216,20 +215,6 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
     it.q_sorted = true;
     it.q_pos0 = w.first;
     it.qt_count = w.count / TILE;
-  } else if (hyper && dual) {
-    // both sampled tiles (slots 0..127 and 128..255) against a chunk of BWD_CHUNK / 2 query tiles
-    const int z = item - items_blk;
-    it.dual = true;
-    it.k_tile = 0;
-    it.krow = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + tid] : tid;
-    it.krow2 = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + TILE + tid] : TILE + tid;
-    it.qt_first = z * (BWD_CHUNK / 2);
-    it.q_len = min((z + 1) * (BWD_CHUNK / 2), n_qt) - it.qt_first;
-    it.qt_count = 2 * it.q_len;
-    if (weighted) {
-      it.q_sorted = true;
-      it.q_pos0 = it.qt_first * TILE;
-    }
   } else {
     const int i2 = hyper ? item - items_blk : item;
     int z;
@@ -261,7 +246,6 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
 // local query row of thread tid in list entry jj of an item (-1: none)
 __device__ __forceinline__ int bwd_q_row(const ha_attn_params& p, const BwdItem& it, int seg, int jj, int tid) {
   if (jj >= it.qt_count) return -1;
-  if (it.dual && jj >= it.q_len) jj -= it.q_len;
   if (it.q_sorted) {
     int pos = it.q_pos0 + (it.paired ? (jj & 1) : jj) * TILE + tid;
     if (pos >= p.m_q) pos -= p.m_q;
@@ -281,7 +265,7 @@ struct BwdWork {
 };
 
 __device__ __forceinline__ BwdWork bwd_work(const ha_attn_params& p, long long w, long long n_work, int items_per_seg, int item_base,
-                                            int items_blk, int n_chunks, int tid, bool weighted, bool paired, bool dual) {
+                                            int items_blk, int n_chunks, int tid, bool weighted, bool paired, bool fused) {
   BwdWork wk;
   wk.valid = w < n_work;
   wk.seg = 0;
@@ -292,7 +276,7 @@ __device__ __forceinline__ BwdWork bwd_work(const ha_attn_params& p, long long w
     wk.seg = (int)(w / items_per_seg);
     wk.item = (int)(w - (long long)wk.seg * items_per_seg) + item_base;
     wk.si = seg_info(p, wk.seg);
-    wk.me = bwd_decode(p, wk.item, wk.seg, items_blk, n_chunks, tid, weighted, paired, dual);
+    wk.me = bwd_decode(p, wk.item, wk.seg, items_blk, n_chunks, tid, weighted, paired, fused);
     wk.qrow0 = bwd_q_row(p, wk.me, wk.seg, 0, tid);
     wk.qrow1 = bwd_q_row(p, wk.me, wk.seg, 1, tid);
   }
@@ -318,10 +302,9 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   const int row = tid & 127, wg = tid >> 7, qwarp = (tid >> 5) & 3;
   const bool hyper = p.mode == HA_MODE_HYPER;
   const bool causal = p.flags & HA_FLAG_CAUSAL;
-  // mode_bits: 1 = block items cover whole 256-row blocks (paired); 2 = ordered dQ: the sampled items run in an earlier
-  // launch, as dual items (both sampled tiles; first tile stores its dQ rows into dq_acc, second adds), and the paired
-  // block items add their single contribution and write the final dq_out rows
-  const bool pair_blocks = Cfg::PIPE && (mode_bits & 1), ordered = Cfg::PIPE && (mode_bits & 2);
+  // mode_bits: 1 = block items cover whole 256-row blocks (paired); 4 = fused: they also take the two sampled key tiles
+  // (no sampled items); 2 = final dQ: a block item then holds a query tile's complete dQ sum and writes the dq_out rows
+  const bool pair_blocks = Cfg::PIPE && (mode_bits & 1), final_dq = Cfg::PIPE && (mode_bits & 2), fuse_sampled = Cfg::PIPE && (mode_bits & 4);
   if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
 
   // ---- once per CTA: barrier, TMEM ----
@@ -376,14 +359,14 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
         if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_Q + Cfg::Q_BYTES, qb, p.q_sn, wk.qrow1, qwarp, lane);
         else bwd_gather_tile<DV>(s_base + Cfg::OFF_DO + Cfg::DO_BYTES, gb, p.do_sn, wk.qrow1, qwarp, lane);
       }
-      if (go && (wk.me.paired || wk.me.dual)) {
+      if (go && wk.me.paired) {
         if (wg == 0) bwd_gather_tile<D>(s_base + Cfg::OFF_K2, kb, p.k_sn, wk.me.krow2, qwarp, lane);
         else bwd_gather_tile<DV>(s_base + Cfg::OFF_V2, vb, p.v_sn, wk.me.krow2, qwarp, lane);
       }
       cp_async_commit();
     }
   };
-  auto next_work = [&](long long w) { return bwd_work(p, w, n_work, items_per_seg, item_base, items_blk, n_chunks, row, WT, pair_blocks, ordered); };
+  auto next_work = [&](long long w) { return bwd_work(p, w, n_work, items_per_seg, item_base, items_blk, n_chunks, row, WT, pair_blocks, fuse_sampled); };
 
   // ---- persistent loop over work items.  A CTA starts with item blockIdx.x and draws every further one from the
   //      launch's counter (items differ in length: 1 to 16 pairs), early in the current item; the next item's first
@@ -400,8 +383,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   const BwdItem me = cur.me;
   const int seg = cur.seg, item = cur.item;
   const SegInfo si = cur.si;
-  const bool paired = Cfg::PIPE && me.paired, dual = Cfg::PIPE && me.dual;
-  const int q_len = me.q_len;
+  const bool paired = Cfg::PIPE && me.paired, fused = Cfg::PIPE && me.fused;
   const int krow = me.krow, qt_first = me.qt_first, qt_count = me.qt_count, k_tile = me.k_tile;
   if (qt_count <= 0) {           // nothing to do for this item (uniform over the CTA): its (empty) copy groups retire
     cp_async_wait<0>();
@@ -472,15 +454,17 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   // P and dS of this thread's query row, its group's 64 key columns -> shared memory
   // weighted sampling (sampled items only): pair jj meets sorted query tile qt_first + jj; its log weight is added to
   // the scores and the dropped slots among this group's 64 key columns give p = 0
-  const bool weighted = WT && hyper && item >= items_blk;
+  const bool weighted = WT && hyper && (item >= items_blk || fused);
   auto elementwise = [&](float lse2, float dlt, bool diag, int jj) {
     const int limit = diag ? row + 1 : TILE;
     uint32_t wm[2] = {0u, 0u};
     float bias2 = 0.f;
-    if (WT && weighted) {
-      const bool second = dual && jj >= q_len;
-      const long long qtile = (long long)seg * (p.m_q / TILE) + qt_first + (second ? jj - q_len : jj);
-      const uint32_t* mw = p.sample_mask + qtile * (p.sample_size / 32) + (dual ? (second ? 1 : 0) : k_tile) * 4 + wg * 2;
+    if (WT && weighted && (!fused || jj >= 4)) {
+      // sorted query tile and sampled tile of this pair (fused item: query tiles 2b, 2b+1 alternate; pairs 4,5 meet
+      // sampled tile 0, pairs 6,7 sampled tile 1)
+      const long long qtile = (long long)seg * (p.m_q / TILE) + (fused ? k_tile + (jj & 1) : qt_first + jj);
+      const int stile = fused ? (jj >> 1) - 2 : k_tile;
+      const uint32_t* mw = p.sample_mask + qtile * (p.sample_size / 32) + stile * 4 + wg * 2;
       wm[0] = mw[0];
       wm[1] = mw[1];
       bias2 = p.sample_logw[qtile] * LOG2E;
@@ -524,19 +508,19 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   // dK / dV rows of a key tile (lanes = keys), one column half per thread group: fp32 reductions into the accumulators
   // (staging rows are private per warp), or -- direct mode -- stored once in the tensors' dtype (block items, which hold
   // the complete block part of their rows) / reduced into the slot-indexed fp32 buffers (sampled items)
-  auto drain_kv = [&](int kr, int tile) {
+  auto drain_kv = [&](int kr, int tile, bool sampled_tile) {
     uint8_t* stg = smem + Cfg::OFF_STG + wg * Cfg::STG_HALF;
     if (p.dk_out == nullptr) {
       float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
       float* dv_base = p.dv_acc + (head0 + si.k_row0) * DV;
-      if (p.flags & HA_FLAG_BWD_KV_INIT) {   // this item is the only writer of its key rows: store, nothing to add to
+      if (p.flags & HA_FLAG_BWD_KV_INIT) {   // (exact attention only) this item is the only writer of its key rows: store, nothing to add to
         reduce_rows<DV / 2, 1>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr, row);
         reduce_rows<D / 2, 1>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr, row);
       } else {
         reduce_rows<DV / 2>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr, row);
         reduce_rows<D / 2>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr, row);
       }
-    } else if (item < items_blk) {
+    } else if (!sampled_tile) {
       T* dk_base = (T*)p.dk_out + (head0 + si.k_row0) * D;
       T* dv_base = (T*)p.dv_out + (head0 + si.k_row0) * DV;
       store_rows<T, DV / 2>(tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr);
@@ -557,17 +541,14 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     // starts as soon as the batch has landed.
     // ------------------------------------------------------------------------------------------------------------
     uint8_t* sSTG = smem + Cfg::OFF_STG;
-    // dQ rows of pair jp (TMEM buffer jp & 1) -> global: fp32 reduction; in ordered mode a first-tile pair of a dual item
-    // stores, and a paired block item (last contribution, its launch runs after the sampled one) writes the final rows
+    // dQ rows of pair jp (TMEM buffer jp & 1) -> global: fp32 reduction into dq_acc, or -- a paired item whose TMEM
+    // buffer holds the query tile's complete sum (final_dq) -- the final rows of dq_out
     auto drain_dq = [&](int jp, int qrow_of_pair) {
       uint8_t* stg = sSTG + wg * Cfg::STG_HALF;
       const uint32_t t_src = tDQ + (jp & 1) * D + lane_sel + wg * (D / 2);
       float* dst = dq_base + wg * (D / 2);
-      if (ordered && paired)
-        reduce_rows<D / 2, 2, T>(stg, t_src, dst, D, qrow_of_pair, row, (T*)p.dq_out + (head0 + si.q_row0) * D + wg * (D / 2),
-                                 p.sample_size > 0);
-      else if (ordered && dual && jp < q_len)
-        reduce_rows<D / 2, 1>(stg, t_src, dst, D, qrow_of_pair, row);
+      if (final_dq && paired)
+        reduce_rows<D / 2, 2, T>(stg, t_src, dst, D, qrow_of_pair, row, (T*)p.dq_out + (head0 + si.q_row0) * D + wg * (D / 2));
       else
         reduce_rows<D / 2>(stg, t_src, dst, D, qrow_of_pair, row);
     };
@@ -596,14 +577,23 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       int qrow_after = -1;
       float lse_after = INFINITY, delta_after = 0.f;
       if (!paired && jj >= 1 && jj + 1 < qt_count) fetch_q(st ^ 1, qrow_next);   // (a paired item keeps both tiles)
+      if (fused && (jj == 2 || jj == 4)) {
+        // the key buffer whose tile is through (A at pair 2, B at pair 4) takes a sampled tile, needed two pairs later
+        const int sr = jj == 2 ? me.srow0 : me.srow1;
+        const uint16_t* kb = (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
+        const uint16_t* vb = (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn;
+        if (wg == 0) bwd_gather_tile<D>(s_base + (jj == 2 ? Cfg::OFF_K : Cfg::OFF_K2), kb, p.k_sn, sr, qwarp, lane);
+        else bwd_gather_tile<DV>(s_base + (jj == 2 ? Cfg::OFF_V : Cfg::OFF_V2), vb, p.v_sn, sr, qwarp, lane);
+      }
       cp_async_commit();
       if (jj + 2 < qt_count) {
         qrow_after = q_row(jj + 2);
       }
       HA_T_MARK(2)
       // paired block item: the first key tile's dV / dK are final once pair 1 is through; pair 2 starts them afresh
-      if (paired && jj == 2) drain_kv(krow, k_tile);
-      if (dual && jj == q_len) drain_kv(krow, 0);
+      if (paired && jj == 2) drain_kv(krow, k_tile, false);
+      if (fused && jj == 4) drain_kv(me.krow2, k_tile + 1, false);
+      if (fused && jj == 6) drain_kv(me.srow0, 0, true);
       elementwise(lse_cur, delta_cur, diag_possible && qt_first + jj == k_tile, jj);
       HA_T_MARK(3)
       cp_async_wait<0>();                     // query tile jj+1 has landed
@@ -614,11 +604,9 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       if (tid == 0) {
         if (paired) {
           // dV / dK restart with each key tile; dQ of a query tile sums over both key tiles in its own TMEM buffer
-          issue_mma2(st, jj & 1, tDQ + (jj & 1) * D, jj >= 2, jj >= 2 ? 1u : 0u);
-          if (jj + 1 < qt_count) issue_mma1(st ^ 1, jj + 1 >= 2);
-        } else if (dual) {
-          issue_mma2(st, jj != 0 && jj != q_len, tDQ + (jj & 1) * D, jj >= q_len);
-          if (jj + 1 < qt_count) issue_mma1(st ^ 1, jj + 1 >= q_len);
+          // (key buffers alternate with the key tile jj / 2: A, B, and -- fused -- S0, S1)
+          issue_mma2(st, jj & 1, tDQ + (jj & 1) * D, (jj >> 1) & 1, jj >= 2 ? 1u : 0u);
+          if (jj + 1 < qt_count) issue_mma1(st ^ 1, ((jj + 1) >> 1) & 1);
         } else {
           issue_mma2(st, jj > 0, tDQ + (jj & 1) * D);
           if (jj + 1 < qt_count) issue_mma1(st ^ 1);
@@ -627,13 +615,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       }
       HA_T_MARK(4)
       // underneath the batch: dQ of the previous pair (paired item: of query tile 0, complete after pair 2)
-      if (jj >= 1 && (!paired || jj == 3)) drain_dq(jj - 1, qrow_prev);
+      if (jj >= 1 && (!paired || jj == qt_count - 1)) drain_dq(jj - 1, qrow_prev);
       HA_T_MARK(5)
-      if (jj == 0 && ordered && paired && p.sample_size > 0) {
-        // the sampled launch's partial dQ rows of both query tiles: into L2 now, read by the final drains
-        if (qrow_cur >= 0) prefetch_l2(dq_base + (int64_t)qrow_cur * D + wg * (D / 2));
-        if (qrow_next >= 0) prefetch_l2(dq_base + (int64_t)qrow_next * D + wg * (D / 2));
-      }
       // rotate the per-tile registers; lse/delta of tile jj+2 are loaded here so that they arrive during the next pair
       qrow_prev = qrow_cur;
       qrow_cur = qrow_next;
@@ -723,7 +706,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     if (tid == 0 && p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
   } else {
     __syncthreads();
-    drain_kv((paired || dual) ? me.krow2 : krow, dual ? 1 : k_tile);
+    drain_kv(fused ? me.srow1 : paired ? me.krow2 : krow, fused ? 1 : paired ? k_tile + 1 : k_tile, fused || (hyper && item >= items_blk));
   }
   HA_T_MARK(7)
   w = failed ? n_work : s_next_w;    // (the slot is rewritten only after the next item's first barrier)
@@ -766,13 +749,16 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   // block size 256 with plain windows on whole blocks: one item per block (both key tiles, both query tiles)
   const int pair_blocks = Cfg::PIPE && p.mode == HA_MODE_HYPER && !(p.flags & HA_FLAG_SMOOTH) && (p.block_size + TILE - 1) / TILE == 2 &&
                           p.m_k % (2 * TILE) == 0;
-  // ordered dQ (dq_out given; tc_bwd_direct_level says when): sampled items first, then the block items
-  const bool ordered = p.dq_out != nullptr;
-  if (ordered && !(pair_blocks && (p.sample_size == 0 || p.sample_size == 2 * TILE))) return HA_ERR_INVALID;
-  const int n_chunks_dual = (n_qt + BWD_CHUNK / 2 - 1) / (BWD_CHUNK / 2);
+  // final dQ rows (dq_out given; tc_bwd_direct_level says when): every query tile's sum must be complete in one item
+  const bool final_dq = p.dq_out != nullptr;
+  if (final_dq && !(pair_blocks && (p.sample_size == 0 || p.sample_size == 2 * TILE))) return HA_ERR_INVALID;
+  // Only with direct outputs: a fused item drains the sampled tiles' dK/dV sums once per block (eight times as often as
+  // a sampled item over 16 query tiles); into the small slot buffers that is affordable, into the fp32 accumulators of
+  // the causal rectangles it costs more than the fusing saves (measured: 31.7 ms against 31.2 ms on the causal step).
+  const int fuse_sampled = pair_blocks && p.sample_size == 2 * TILE && p.dk_out != nullptr;
   if (p.mode == HA_MODE_HYPER) {
     items_blk = pair_blocks ? n_kt / 2 : n_kt;
-    items = (long long)items_blk + (long long)(p.sample_size / TILE) * n_chunks;
+    items = (long long)items_blk + (fuse_sampled ? 0 : (long long)(p.sample_size / TILE) * n_chunks);
   } else {
     items = (long long)n_kt * n_chunks;
   }
@@ -795,14 +781,10 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
     return HA_OK;
   };
   int lrc;
-  if (ordered) {
-    if (p.sample_size > 0) {
-      if ((lrc = launch(n_chunks_dual, 3, items_blk)) != HA_OK) return lrc;
-      HA_LAUNCHED("ha_attn_bwd (tcgen05, sampled items)");
-    }
-    if ((lrc = launch(items_blk, 3, 0)) != HA_OK) return lrc;
+  if (fuse_sampled) {
+    if ((lrc = launch(items_blk, 1 | 4 | (final_dq ? 2 : 0), 0)) != HA_OK) return lrc;
   } else {
-    if ((lrc = launch(items, pair_blocks, 0)) != HA_OK) return lrc;
+    if ((lrc = launch(items, (pair_blocks ? 1 : 0) | (final_dq ? 2 : 0), 0)) != HA_OK) return lrc;
   }
   HA_LAUNCHED("ha_attn_bwd (tcgen05)");
   return HA_OK;

@@ -281,8 +281,8 @@ def hyper_bwd(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, s
         segs = B * H
         out = torch.empty(r * (2 * d + dv), dtype=q.dtype, device=dev)           # dq | dk | dv
         sacc = torch.zeros(max(1, segs * sample_size * (d + dv)), dtype=torch.float32, device=dev)
-        # level 2: dq_acc is scratch the kernels initialise themselves; level 1: a zeroed accumulator, cast afterwards
-        dq_acc = (torch.empty if level == 2 else torch.zeros)(r * d, dtype=torch.float32, device=dev)
+        # level 2: dq rows are written directly; level 1: a zeroed fp32 accumulator, cast afterwards
+        dq_acc = torch.zeros(r * d, dtype=torch.float32, device=dev) if level == 1 else None
         es = out.element_size()
         p.dq_acc = _ptr(dq_acc)
         p.dk_out, p.dv_out = C.c_void_p(out.data_ptr() + es * r * d), C.c_void_p(out.data_ptr() + es * 2 * r * d)
@@ -306,7 +306,7 @@ def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sa
     """One ha_attn_bwd call (HA_MODE_HYPER) on [B, n, H, *] views and nothing else.  acc = zeroed fp32 buffer holding
     dq | dk | dv accumulators ([B,H,n,d], [B,H,n,d], [B,H,n,dv] back to back); with direct_out = (out, sacc) -- `out` in
     the input dtype holding dq | dk | dv, `sacc` the zeroed fp32 slot buffers [B*H*S*(d+dv)] -- only the dq part of acc is
-    used (as scratch where the library writes dq directly, else as the zeroed accumulator)."""
+    used, and only where the library cannot write dq directly."""
     B, n, H, d = q.shape
     r = B * H * n
     p = _bwd_params(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, scale, flags, weights)

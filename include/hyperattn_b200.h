@@ -155,9 +155,10 @@ typedef struct {
    * (src/hyper_attn_triton.py:399-506, :517-665). */
   void *dk_out, *dv_out;
   float *dk_sacc, *dv_sacc;
-  /* direct dQ (only where ha_attn_bwd_direct_level says 2; together with dk_out / dv_out): the sampled work items run
-   * first and leave their sum in dq_acc (fp32 scratch, need NOT be zeroed), the block items then add their single
-   * contribution per query row and write dq_out ([B,H,n,d] contiguous, dtype rows): no zero-fill, no cast pass. */
+  /* direct dQ (only where ha_attn_bwd_direct_level says 2; together with dk_out / dv_out): every query tile's dQ is summed
+   * inside one work item (a 256-row block's two key tiles and the two sampled key tiles against its two query tiles) and
+   * written once to dq_out ([B,H,n,d] contiguous, dtype rows): no fp32 accumulator, zero-fill or cast pass; dq_acc is
+   * not used and may be NULL. */
   void* dq_out;
 } ha_attn_params;
 
