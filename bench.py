@@ -277,11 +277,11 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM traffic of the dominant kernel (attn_tc_bwd_kernel, hyper pattern: its two launches per backward, sampled items then
-# block items), from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of the 8-head x 65536-token case, which
-# scales linearly with the number of rows (fixed work per row): 159.1 + 411.3 MB read, 92.7 + 160.3 MB written for
-# 524288 rows.  Summary of the capture: profiles/attn_tc_bwd_kernel_hyper_8x65536.md.
-BWD_DRAM_BYTES_PER_ROW = 1570.0
+# DRAM traffic of the dominant kernel (attn_tc_bwd_kernel, hyper pattern: one launch per backward, fused block + sampled
+# work items), from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of the 8-head x 65536-token case, which
+# scales linearly with the number of rows (fixed work per row): 278.6 MB read, 161.4 MB written for 524288 rows.
+# Summary of the capture: profiles/attn_tc_bwd_kernel_hyper_8x65536.md.
+BWD_DRAM_BYTES_PER_ROW = 839.0
 
 
 def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
@@ -336,7 +336,7 @@ def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
         r_['frac'] = r_['achieved'] / r_['peak']
     out['stage_rooflines'] = st
     ach = tf(fl_bwd, t_bwd)
-    out['roofline'] = {'bound': 'tensor', 'kernel': 'attn_tc_bwd_kernel (hyper pattern: both launches of one backward, sampled items then block items; the longest kernel of the step)', 'achieved': ach,
+    out['roofline'] = {'bound': 'tensor', 'kernel': 'attn_tc_bwd_kernel (hyper pattern, one launch per backward; the longest kernel of the step)', 'achieved': ach,
                        'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s', 'frac': ach / peaks['bf16_tflops'],
                        'traffic': BWD_DRAM_BYTES_PER_ROW * rows if BWD_DRAM_BYTES_PER_ROW else None,
                        'peak_source': peaks['src'], 'launch_ms': t_bwd, 'algorithmic_flops_per_launch': fl_bwd,
