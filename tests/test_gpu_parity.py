@@ -345,7 +345,9 @@ def test_hyper_attn_rejects_bad_shapes(ha):
 # ------------------------------------------------------------------------------------------------ exact attention op
 @pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize('cfg', [(1, 2, 256, 64, True), (2, 2, 200, 64, True), (1, 1, 384, 128, False), (1, 3, 77, 32, False),
-                                 (1, 2, 1024, 64, True)])
+                                 (1, 2, 1024, 64, True),
+                                 (1, 1, 4608, 64, True),      # 36 query tiles: three chunks per key tile, some of them empty
+                                 (1, 1, 2304, 64, False)])
 def test_flash_fwd_bwd_vs_oracle(ha, dtype, cfg):
     B, H, n, d, causal = cfg
     torch.manual_seed(20)
