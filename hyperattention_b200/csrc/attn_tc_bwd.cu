@@ -543,14 +543,24 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     uint8_t* sSTG = smem + Cfg::OFF_STG;
     // dQ rows of pair jp (TMEM buffer jp & 1) -> global: fp32 reduction into dq_acc, or -- a paired item whose TMEM
     // buffer holds the query tile's complete sum (final_dq) -- the final rows of dq_out
-    auto drain_dq = [&](int jp, int qrow_of_pair) {
-      uint8_t* stg = sSTG + wg * Cfg::STG_HALF;
-      const uint32_t t_src = tDQ + (jp & 1) * D + lane_sel + wg * (D / 2);
-      float* dst = dq_base + wg * (D / 2);
-      if (final_dq && paired)
-        reduce_rows<D / 2, 2, T>(stg, t_src, dst, D, qrow_of_pair, row, (T*)p.dq_out + (head0 + si.q_row0) * D + wg * (D / 2));
-      else
-        reduce_rows<D / 2>(stg, t_src, dst, D, qrow_of_pair, row);
+    // under_batch: the drain runs while the batch issued just before executes.  The thread that issued it is held by the
+    // tensor pipe for about as long as the batch takes, so its warp's share of the drain would come after everybody
+    // else's and delay the next pair: the warp of the other group that sits on the same 32 TMEM lanes takes both
+    // column halves of those rows instead.
+    auto drain_dq = [&](int jp, int qrow_of_pair, bool under_batch) {
+      if (final_dq && paired) {
+        reduce_rows<D / 2, 2, T>(sSTG + wg * Cfg::STG_HALF, tDQ + (jp & 1) * D + lane_sel + wg * (D / 2), dq_base + wg * (D / 2), D,
+                                 qrow_of_pair, row, (T*)p.dq_out + (head0 + si.q_row0) * D + wg * (D / 2));
+        return;
+      }
+      const int warp_id = tid >> 5;
+      if (under_batch && warp_id == 0) return;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (half != wg && !(under_batch && warp_id == 4)) continue;
+        reduce_rows<D / 2>(sSTG + half * Cfg::STG_HALF, tDQ + (jp & 1) * D + lane_sel + half * (D / 2), dq_base + half * (D / 2), D,
+                           qrow_of_pair, row);
+      }
     };
     float lse_next = INFINITY, delta_next = 0.f;
     if (qt_count > 1 && qrow_next >= 0) { lse_next = lse_base[qrow_next] * LOG2E; delta_next = delta_base[qrow_next]; }
@@ -615,7 +625,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       }
       HA_T_MARK(4)
       // underneath the batch: dQ of the previous pair (paired item: of query tile 0, complete after pair 2)
-      if (jj >= 1 && (!paired || jj == qt_count - 1)) drain_dq(jj - 1, qrow_prev);
+      if (jj >= 1 && (!paired || jj == qt_count - 1)) drain_dq(jj - 1, qrow_prev, true);
       HA_T_MARK(5)
       // rotate the per-tile registers; lse/delta of tile jj+2 are loaded here so that they arrive during the next pair
       qrow_prev = qrow_cur;
@@ -638,7 +648,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     HA_T_MARK(6)
     if (!failed) {
       issue_loads(nxt);                              // every operand tile is free now
-      drain_dq(qt_count - 1, qrow_prev);
+      drain_dq(qt_count - 1, qrow_prev, false);
     }
   } else {
     // ------------------------------------------------------------------------------------------------------------
