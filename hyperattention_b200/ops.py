@@ -310,8 +310,10 @@ def hyper_bwd_launch(q, k, v, qi, ki, si, o, lse, do, delta, acc, block_size, sa
     B, n, H, d = q.shape
     r = B * H * n
     p = _bwd_params(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size, scale, flags, weights)
-    p.dq_acc, p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr()), C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
-    if direct_out is not None:
+    p.dq_acc = C.c_void_p(acc.data_ptr())
+    if direct_out is None:
+        p.dk_acc, p.dv_acc = C.c_void_p(acc.data_ptr() + 4 * r * d), C.c_void_p(acc.data_ptr() + 8 * r * d)
+    else:
         out, sacc = direct_out
         es = out.element_size()
         p.dk_out, p.dv_out = C.c_void_p(out.data_ptr() + es * r * d), C.c_void_p(out.data_ptr() + es * 2 * r * d)
