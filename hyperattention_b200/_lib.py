@@ -16,7 +16,8 @@ FLAG_CAUSAL, FLAG_SMOOTH, FLAG_MERGE, FLAG_MERGE_EXACT, FLAG_BWD_REF_SMOOTH, FLA
 
 _STATUS = {-1: 'invalid argument (shape / stride / size not accepted)', -2: 'unsupported dtype',
            -3: 'workspace missing or too small', -4: 'CUDA runtime error', 1: 'device-side wait timed out',
-           -5: 'needs more scratch than the library\'s built-in array holds (use the entry point that takes a workspace)'}
+           -5: 'beyond a size limit of this entry point (too many segments / work items for one launch, or -- '
+               'ha_seg_sort_noalloc -- more scratch than the built-in array holds: use ha_seg_sort with a workspace)'}
 
 i32, i64, f32, vp = C.c_int32, C.c_int64, C.c_float, C.c_void_p
 
@@ -35,7 +36,7 @@ class AttnParams(C.Structure):
         ('lse', vp), ('part_o', vp), ('part_lse', vp),
         ('d_o', vp), ('do_sb', i64), ('do_sh', i64), ('do_sn', i64),
         ('delta', vp), ('dq_acc', vp), ('dk_acc', vp), ('dv_acc', vp),
-        ('status', vp),
+        ('status', vp), ('status_host', vp),
         ('sample_logw', vp), ('sample_mask', vp),
         ('dk_out', vp), ('dv_out', vp), ('dk_sacc', vp), ('dv_sacc', vp), ('dq_out', vp),
     ]
@@ -46,10 +47,10 @@ class CausalParams(C.Structure):
         ('dtype', i32), ('flags', i32),
         ('B', i32), ('H', i32), ('n', i32), ('d', i32), ('dv', i32),
         ('levels', i32), ('block_size', i32), ('sample_size', i32), ('lsh_bits', i32), ('keep_parts', i32),
-        ('scale', f32),
+        ('min_seq_len', i32), ('scale', f32),
         ('q', vp), ('k', vp), ('v', vp), ('proj', vp), ('o', vp), ('lse', vp),
         ('saved', vp), ('saved_bytes', i64), ('scratch', vp), ('scratch_bytes', i64),
-        ('d_o', vp), ('dq', vp), ('dk', vp), ('dv_out', vp), ('status', vp),
+        ('d_o', vp), ('dq', vp), ('dk', vp), ('dv_out', vp), ('status', vp), ('status_host', vp),
     ]
 
 
@@ -71,6 +72,7 @@ SIGNATURES = {
     'ha_delta': (C.c_int, [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, i32, vp, vp]),
     'ha_cast_from_f32': (C.c_int, [vp, vp, i64, i32, vp]),
     'ha_lse_merge': (C.c_int, [vp, vp, vp, vp, i64, i32, i32, i32, vp]),
+    'ha_wait_probe': (C.c_int, [vp, vp, i32, vp]),
     'ha_causal_saved_bytes': (i64, [C.POINTER(CausalParams)]),
     'ha_causal_scratch_bytes': (i64, [C.POINTER(CausalParams), i32]),
     'ha_causal_fwd': (C.c_int, [C.POINTER(CausalParams), vp]),

@@ -73,6 +73,25 @@ __global__ void bwd_finish_kernel(const ha_attn_params p, long long total) {
   for (int j = 0; j < 8; ++j) v[j] = from_f32<T>(to_f32<T>(v[j]) + a[j]);
   *reinterpret_cast<uint4*>(out) = raw;
 }
+
+// One warp, one mbarrier that nobody arrives at: the wait runs out after `polls` polls and is reported like any other.
+__global__ void wait_probe_kernel(int32_t* status, int32_t* status_host, int polls) {
+  __shared__ uint64_t bar_mem;
+  const uint32_t bar = smem_u32(&bar_mem);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  bool done = false;
+  for (int i = 0; i < polls && !done; ++i) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(0u) : "memory");
+    done = ok != 0;
+  }
+  if (!done && threadIdx.x == 0) report_timeout(status, status_host);
+}
 }  // namespace ha
 
 using namespace ha;
@@ -109,6 +128,13 @@ int ha_attn_bwd_direct_level(const ha_attn_params* p) {
   const bool whole_blocks = !(p->flags & HA_FLAG_SMOOTH) && (p->block_size + TILE - 1) / TILE == 2 && p->m_k % (2 * TILE) == 0;
   if (p->d == 64 && p->dv == 64 && whole_blocks && (p->sample_size == 0 || p->sample_size == 2 * TILE)) return 2;
   return 1;
+}
+
+int ha_wait_probe(int32_t* status, int32_t* status_host, int32_t polls, void* stream) {
+  if ((!status && !status_host) || polls < 1 || polls > SPIN_LIMIT) return HA_ERR_INVALID;
+  wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, status_host, polls);
+  HA_LAUNCHED("ha_wait_probe");
+  return HA_OK;
 }
 
 int ha_attn_bwd_finish(const ha_attn_params* p, void* stream) {

@@ -295,6 +295,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   __shared__ uint64_t mma_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ long long s_next_w;     // the work item this CTA takes next (fetched by thread 0 from the launch's counter)
+  __shared__ int s_bail;
 
   // 256 threads = two groups of 128.  Thread (wg, row): TMEM lane `row`; in the elementwise phase group wg handles key
   // columns [64 wg, 64 wg + 64) of that row, in the reductions the column half wg of its row.
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   // mode_bits: 1 = block items cover whole 256-row blocks (paired); 4 = fused: they also take the two sampled key tiles
   // (no sampled items); 2 = final dQ: a block item then holds a query tile's complete dQ sum and writes the dq_out rows
   const bool pair_blocks = Cfg::PIPE && (mode_bits & 1), final_dq = Cfg::PIPE && (mode_bits & 2), fuse_sampled = Cfg::PIPE && (mode_bits & 4);
-  if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
+  if (cta_sees_failure(p.status, &s_bail)) return;   // an earlier CTA gave up: drain quickly (uniform over the CTA)
 
   // ---- once per CTA: barrier, TMEM ----
   const uint32_t bar = smem_u32(&mma_bar);
@@ -713,7 +714,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   }
 
   if (failed) {
-    if (tid == 0 && p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
+    if (tid == 0) report_timeout(p.status, p.status_host);
   } else {
     __syncthreads();
     drain_kv(fused ? me.srow1 : paired ? me.krow2 : krow, fused ? 1 : paired ? k_tile + 1 : k_tile, fused || (hyper && item >= items_blk));
@@ -772,7 +773,7 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
   } else {
     items = (long long)n_kt * n_chunks;
   }
-  if (items > 0x7fffffffLL || segs > 65535) return HA_ERR_INVALID;
+  if (items > 0x7fffffffLL) return HA_ERR_INVALID;
   HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_bwd_kernel<T, D, DV, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
              "ha_attn_bwd smem attribute");
   int dev = 0, sms = 148;

@@ -94,6 +94,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   const uint32_t s_base = smem_u32(smem);
   __shared__ uint64_t mma_bar;
   __shared__ uint32_t tmem_slot;
+  __shared__ int s_bail;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool hyper = p.mode == HA_MODE_HYPER;
@@ -106,7 +107,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   const uint32_t bar = smem_u32(&mma_bar);
   HA_T_DECL(8)
 
-  if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
+  if (cta_sees_failure(p.status, &s_bail)) return;   // an earlier CTA gave up: drain quickly (uniform over the CTA)
   if (tid == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
@@ -410,7 +411,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   }
 
   if (failed) {
-    if (tid == 0 && p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
+    if (tid == 0) report_timeout(p.status, p.status_host);
   } else {
     // ---- epilogue ----
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;

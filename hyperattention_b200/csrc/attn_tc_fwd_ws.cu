@@ -64,13 +64,14 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
   __shared__ uint64_t bars[N_BARS];
   __shared__ uint32_t tmem_slot;
   __shared__ int s_abort;
+  __shared__ int s_bail;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   constexpr bool merge = MG;
   const int n_blk = 2;                                   // window tiles of a block (block size rounded up to 256)
   const int n_tiles = n_blk + p.sample_size / TILE;      // key tiles per item
 
-  if (p.status && *reinterpret_cast<volatile int32_t*>(p.status) != 0) return;   // an earlier CTA gave up: drain quickly
+  if (cta_sees_failure(p.status, &s_bail)) return;   // an earlier CTA gave up: drain quickly (uniform over the CTA)
   auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
   if (tid == 0) {
     // arrivals per phase: 32 (every loader lane, when its copies have landed) on the "full" barriers, 128 (a softmax
@@ -94,7 +95,7 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
     if (*reinterpret_cast<volatile int*>(&s_abort)) return false;
     if (mbar_wait(bar(b), parity)) return true;
     *reinterpret_cast<volatile int*>(&s_abort) = 1;
-    if (p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
+    report_timeout(p.status, p.status_host);
     return false;
   };
 
@@ -451,7 +452,7 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
         if (progressed) idle = 0;
         else if (++idle > idle_limit || *reinterpret_cast<volatile int*>(&s_abort)) {
           *reinterpret_cast<volatile int*>(&s_abort) = 1;
-          if (p.status) atomicExch(p.status, HA_DEV_TIMEOUT);
+          report_timeout(p.status, p.status_host);
           ok = false;
         }
       }

@@ -18,7 +18,8 @@ namespace ha {
 bool tc_bwd_supported(const ha_attn_params& p);   // attn_tc_bwd.cu
 
 // One helper stream and two events per device, created on first use and kept for the life of the process.
-struct SideStream { cudaStream_t stream; cudaEvent_t fork, join; };
+// `mu` serialises the callers of one device over the fork .. join section (the two events are shared).
+struct SideStream { cudaStream_t stream; cudaEvent_t fork, join; std::mutex* mu; };
 static SideStream* side_stream() {
   static std::mutex mu;
   static SideStream per_dev[64];
@@ -34,6 +35,7 @@ static SideStream* side_stream() {
     if (cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, prio_hi) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    s.mu = new std::mutex();
     per_dev[dev] = s;
     ready[dev] = true;
   }
@@ -55,8 +57,11 @@ static int make_plan(const ha_causal_params& p, CausalPlan& pl) {
   if (p.n % (1 << p.levels) != 0) return HA_ERR_INVALID;
   if (p.sample_size < 0 || p.sample_size % TILE != 0 || p.block_size < 1) return HA_ERR_INVALID;
   pl.leaf = p.n >> p.levels;
-  // every rectangle must be a whole number of 128-row tiles and hold the sampled rows
-  if (pl.leaf % TILE != 0 || p.sample_size > pl.leaf) return HA_ERR_INVALID;
+  // every rectangle must be a whole number of 128-row tiles, and those on the hyper pattern must hold the sampled rows
+  // (the deepest ones are exact where they are shorter than min_seq_len)
+  if (pl.leaf % TILE != 0) return HA_ERR_INVALID;
+  const bool deepest_is_exact = p.min_seq_len > pl.leaf;
+  if (!(deepest_is_exact && p.levels == 1) && p.sample_size > (deepest_is_exact ? 2 * pl.leaf : pl.leaf)) return HA_ERR_INVALID;
   pl.rows = (long long)p.B * p.H * p.n;
   pl.idx_bytes = pl.rows / 2 * 4;
   pl.part_o_bytes = pl.rows * p.dv * dtype_size(p.dtype);
@@ -155,7 +160,12 @@ static void fill_attn(const ha_causal_params& p, ha_attn_params& a) {
   a.lse = p.lse;
   a.d_o = p.d_o; a.do_sn = p.dv; a.do_sh = a.v_sh; a.do_sb = a.v_sb;
   a.status = p.status;
+  a.status_host = p.status_host;
 }
+
+// The deepest rectangles (n / 2^levels rows a side) are exact where they are shorter than min_seq_len, as in the
+// reference's forward_no_causal_mask (hyper_attention.py:109-113).
+static bool deepest_exact(const ha_causal_params& p, const CausalPlan& pl) { return p.min_seq_len > pl.leaf; }
 
 }  // namespace ha
 
@@ -201,13 +211,17 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
   // rectangle) underneath the leaves' kernel, which does not need them.  36 short launches leave the critical path.
   SideStream* side = side_stream();
   cudaStream_t main_st = (cudaStream_t)stream;
+  const bool exact_deepest = deepest_exact(p, pl);
+  // two host threads driving one device share the side stream and its events: one caller at a time from fork to join
+  std::unique_lock<std::mutex> side_lock;
+  if (side) side_lock = std::unique_lock<std::mutex>(*side->mu);
   if (side) {
     HA_CUDA_OK(cudaEventRecord(side->fork, main_st), "ha_causal_fwd fork");
     HA_CUDA_OK(cudaStreamWaitEvent(side->stream, side->fork, 0), "ha_causal_fwd fork");
   }
   void* sort_stream = side ? (void*)side->stream : stream;
   int sort_rc = HA_OK;
-  for (int l = p.levels - 1; l >= 0 && sort_rc == HA_OK; --l) {
+  for (int l = p.levels - 1 - (exact_deepest ? 1 : 0); l >= 0 && sort_rc == HA_OK; --l) {
     const int span = p.n >> l, m = span / 2;
     sort_rc = ha_seg_sort(codes_q, p.B * p.H, p.n, span, m, m, p.lsh_bits, sv.q_idx(l), sort_ws, pl.sort_ws, sort_stream);
     if (sort_rc == HA_OK)
@@ -231,15 +245,17 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
   if (p.keep_parts) { a.part_o = sv.part_o(p.levels); a.part_lse = sv.part_lse(p.levels); }
   rc = ha_attn_fwd(&a, stream);
   if (side) HA_CUDA_OK(cudaStreamWaitEvent(main_st, side->join, 0), "ha_causal_fwd join");
+  if (side) side_lock.unlock();
   if (rc != HA_OK) return rc;
 
   for (int l = p.levels - 1; l >= 0; --l) {
     const int span = p.n >> l, m = span / 2;
-    a.mode = HA_MODE_HYPER;
-    a.flags = HA_FLAG_MERGE | (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_MERGE_EXACT | HA_FLAG_FORCE_SIMT | HA_FLAG_NO_WS));
+    const bool exact = exact_deepest && l == p.levels - 1;
+    a.mode = exact ? HA_MODE_FLASH : HA_MODE_HYPER;
+    a.flags = HA_FLAG_MERGE | (p.flags & (HA_FLAG_MERGE_EXACT | HA_FLAG_FORCE_SIMT)) | (exact ? 0 : (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_NO_WS)));
     a.segs_per_head = 1 << l;
     a.span = span; a.q_off = m; a.k_off = 0; a.m_q = m; a.m_k = m;
-    a.q_idx = sv.q_idx(l); a.k_idx = sv.k_idx(l); a.sample_idx = nullptr;
+    a.q_idx = exact ? nullptr : sv.q_idx(l); a.k_idx = exact ? nullptr : sv.k_idx(l); a.sample_idx = nullptr;
     if (p.keep_parts) { a.part_o = sv.part_o(l); a.part_lse = sv.part_lse(l); }
     rc = ha_attn_fwd(&a, stream);
     if (rc != HA_OK) return rc;
@@ -321,11 +337,12 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
     const int span = p.n >> l, m = span / 2;
     rc = part_delta(l);
     if (rc != HA_OK) return rc;
-    a.mode = HA_MODE_HYPER;
-    a.flags = p.flags & (HA_FLAG_SMOOTH | HA_FLAG_BWD_REF_SMOOTH | HA_FLAG_FORCE_SIMT);
+    const bool exact = deepest_exact(p, pl) && l == p.levels - 1;
+    a.mode = exact ? HA_MODE_FLASH : HA_MODE_HYPER;
+    a.flags = exact ? (p.flags & HA_FLAG_FORCE_SIMT) : (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_BWD_REF_SMOOTH | HA_FLAG_FORCE_SIMT));
     a.segs_per_head = 1 << l;
     a.span = span; a.q_off = m; a.k_off = 0; a.m_q = m; a.m_k = m;
-    a.q_idx = sv.q_idx(l); a.k_idx = sv.k_idx(l); a.sample_idx = nullptr;
+    a.q_idx = exact ? nullptr : sv.q_idx(l); a.k_idx = exact ? nullptr : sv.k_idx(l); a.sample_idx = nullptr;
     rc = ha_attn_bwd(&a, stream);
     if (rc != HA_OK) return rc;
   }

@@ -238,6 +238,23 @@ static __device__ unsigned long long* g_timing_buf = nullptr;   // one per trans
 #define HA_T_DUMP(n, cta, cond)
 #endif
 
+// A bounded wait gave up: record it in the device status word and, if the caller gave one, in the host-visible word.
+__device__ __forceinline__ void report_timeout(int32_t* status, int32_t* status_host) {
+  if (status) atomicExch(status, HA_DEV_TIMEOUT);
+  if (status_host) {
+    *reinterpret_cast<volatile int32_t*>(status_host) = HA_DEV_TIMEOUT;
+    __threadfence_system();
+  }
+}
+// Did an earlier CTA of this (or a previous) launch give up?  One thread reads the word and the whole CTA branches on
+// the shared copy, so the answer is the same for every thread even while another CTA is writing the word.
+// Contains a __syncthreads(): call it from every thread of the CTA.
+__device__ __forceinline__ bool cta_sees_failure(const int32_t* status, int* s_flag) {
+  if (threadIdx.x == 0) *s_flag = status ? *reinterpret_cast<const volatile int32_t*>(status) : 0;
+  __syncthreads();
+  return *s_flag != 0;
+}
+
 // pulls the 128-byte line holding `p` into L2 without blocking the thread
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 

@@ -23,7 +23,8 @@ from . import ops
 class HostStream:
     """Streams [B, H, n, d] host tensors through `module` (a HyperAttention on a CUDA device) in chunks of heads.
 
-    heads_per_chunk: heads per chunk (default: chosen so that a chunk's inputs are about 256 MB).
+    heads_per_chunk: heads per chunk (default: at least four chunks per call, so that copy-in, kernels and copy-out
+    overlap, and at most about 256 MB of inputs per chunk).
     Two chunks of inputs are resident at a time; outputs are written into pinned host buffers that are kept and
     reused between calls (pass out=... to supply your own)."""
 
@@ -48,7 +49,7 @@ class HostStream:
         hpc = self.heads_per_chunk
         if hpc is None:
             per_head = max(1, B * n * d * q.element_size() * n_inputs)
-            hpc = max(1, min(H, (256 << 20) // per_head))
+            hpc = max(1, min(max(1, H // 4), (256 << 20) // per_head))
         return [(h0, min(H, h0 + hpc)) for h0 in range(0, H, hpc)]
 
     def _host_out(self, key, like, shape):
@@ -82,7 +83,12 @@ class HostStream:
             with torch.cuda.stream(s_in):
                 if c >= 2:
                     s_in.wait_event(computed[c - 2])     # at most two chunks of inputs are resident
-                dev_in = [t[:, h0:h1].to(self.device, non_blocking=True) for t in host_in]
+                # one copy per batch index: t[b, h0:h1] is contiguous, t[:, h0:h1] is not when B > 1 (a strided host
+                # slice would go through a pageable temporary and block)
+                dev_in = [torch.empty((B, h1 - h0) + tuple(t.shape[2:]), dtype=t.dtype, device=self.device) for t in host_in]
+                for dst, t in zip(dev_in, host_in):
+                    for b in range(B):
+                        dst[b].copy_(t[b, h0:h1], non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(s_in)
             staged[c] = (dev_in, ev)
@@ -111,7 +117,8 @@ class HostStream:
                     s_out.wait_event(ev_c)
                     for dst, src in zip(out, res):
                         src.record_stream(s_out)
-                        dst[:, h0:h1].copy_(src, non_blocking=True)
+                        for b in range(B):
+                            dst[b, h0:h1].copy_(src[b], non_blocking=True)
                 del dev_in, res
             for s in (s_in, s_comp, s_out):
                 caller.wait_stream(s)

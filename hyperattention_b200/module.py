@@ -105,20 +105,23 @@ class HyperAttention(torch.nn.Module):
         return levels
 
     def _regular_causal(self, n):
-        """True when the single-call schedule applies: n halves evenly down to leaves <= min_seq_len and every
-        rectangle is a whole number of 128-row tiles that holds the sampled rows."""
+        """True when the single-call schedule applies: n halves evenly down to leaves <= min_seq_len, every rectangle is
+        a whole number of 128-row tiles and those on the hyper pattern hold the sampled rows.  (Rectangles shorter than
+        min_seq_len -- only the deepest ones can be -- are exact, hyper_attention.py:109-113; the schedule does the same.)"""
         levels = self._causal_levels(n)
         leaf = n >> levels
-        return levels >= 1 and leaf <= self.min_seq_len and leaf % 128 == 0 and self.sample_size <= leaf \
-            and self.sample_size % 128 == 0
+        smallest_hyper = 2 * leaf if self.min_seq_len > leaf else leaf
+        return levels >= 1 and leaf <= self.min_seq_len and leaf % 128 == 0 and self.sample_size % 128 == 0 \
+            and (self.sample_size <= smallest_hyper or (levels == 1 and self.min_seq_len > leaf))
 
     def forward(self, query: torch.tensor, key: torch.tensor, value: torch.tensor, scale=None, causal=False,
                 return_lse=False):
         """query, key [B, H, n, d]; value [B, H, n, dv]; returns attn [B, H, n, dv] (and lse, float32 [B, H, n, 1];
         [B, H, ceil(n/128)*128] when a causal call is short enough to be a single exact leaf, as in the reference)."""
-        query = query.contiguous()
-        key = key.contiguous()
-        value = value.contiguous()
+        # The reference copies its inputs here (hyper_attention.py:38-40).  The kernels take (batch, head, row) strides,
+        # so only a tensor whose rows are not contiguous is copied; the causal schedule below, which addresses
+        # [B, H, n, d] memory directly, makes its own copies where it needs them.
+        query, key, value = [t if t.stride(-1) == 1 else t.contiguous() for t in (query, key, value)]
         n_query = query.shape[2]
         batch_size, n_heads, n_key, dim = key.shape
         scale = scale or dim ** (-0.5)
@@ -133,10 +136,10 @@ class HyperAttention(torch.nn.Module):
         elif self.fused_causal and self.sampling == 'reference' and self._regular_causal(n_key):
             attn, lse = ops.CausalHyperFunc.apply(query, key, value, self.lsh.proj_f32(), self._causal_levels(n_key),
                                                   self.block_size, self.sample_size, scale, self._flags(),
-                                                  self.grad_mode == 'reference')
+                                                  self.grad_mode == 'reference', self.min_seq_len)
             lse = lse.unsqueeze(-1)
         else:
-            attn, lse = self._causal_by_levels(query, key, value, scale)
+            attn, lse = self._causal_by_levels(query.contiguous(), key.contiguous(), value.contiguous(), scale)
         if not return_lse:
             return attn
         return attn, lse

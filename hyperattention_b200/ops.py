@@ -31,21 +31,47 @@ def _ptr(t):
 _STATUS = {}
 
 
-def _status_word(device):
-    """One int32 per device that the kernels set when a bounded device-side wait expires (0 = healthy)."""
+def _status_words(device):
+    """Per device: the int32 word in device memory that the kernels set when a bounded device-side wait expires
+    (0 = healthy; CTAs that start later see it and return at once), and its twin in pinned host memory, which the
+    kernels write as well and the host can read without synchronising."""
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     if key not in _STATUS:
-        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=f'cuda:{key}')
+        _STATUS[key] = (torch.zeros(1, dtype=torch.int32, device=f'cuda:{key}'),
+                        torch.zeros(1, dtype=torch.int32).pin_memory())
     return _STATUS[key]
+
+
+def _status_word(device):
+    return _status_words(device)[0]
+
+
+def _set_status(p, device):
+    """Fills the status pointers of a parameter struct.  Before that, looks at the host-visible word: a timeout
+    reported by an earlier launch raises here, at the next call into the library, instead of going unnoticed (the
+    outputs of the launch that timed out, and of everything launched since, are undefined)."""
+    dev_w, host_w = _status_words(device)
+    _raise_if_failed(dev_w, host_w)
+    p.status, p.status_host = _ptr(dev_w), C.c_void_p(host_w.data_ptr())
+
+
+def _raise_if_failed(dev_w, host_w):
+    v = int(host_w[0])
+    if v != 0:
+        host_w.zero_()
+        dev_w.zero_()
+        raise RuntimeError(f'hyperattention_b200: a device-side wait timed out in an earlier launch (status {v}); '
+                           'results produced since then are undefined')
 
 
 def check_device_status(device=None, reset=True):
     """Synchronises and raises if a kernel reported a timeout since the last check."""
-    w = _status_word(device if device is not None else torch.cuda.current_device())
-    v = int(w.item())
+    dev_w, host_w = _status_words(device if device is not None else torch.cuda.current_device())
+    v = int(dev_w.item()) | int(host_w[0])
     if v != 0:
         if reset:
-            w.zero_()
+            dev_w.zero_()
+            host_w.zero_()
         raise RuntimeError(f'hyperattention_b200: device-side wait timed out (status {v})')
 
 
@@ -206,7 +232,7 @@ class HyperAttnFunc(torch.autograd.Function):
         p.o = _ptr(o)
         p.o_sb, p.o_sh, p.o_sn = _bhn(o)
         p.lse = _ptr(lse)
-        p.status = _ptr(_status_word(q.device))
+        _set_status(p, q.device)
         wts = None
         if weighted and sample_size > 0:
             # importance-weighted sampled columns, the query tile's own block excluded (not in the reference's code)
@@ -258,7 +284,7 @@ def _bwd_params(q, k, v, qi, ki, si, o, lse, do, delta, block_size, sample_size,
     p.d_o = _ptr(do)
     p.do_sb, p.do_sh, p.do_sn = _bhn(do)
     p.delta = _ptr(delta)
-    p.status = _ptr(_status_word(q.device))
+    _set_status(p, q.device)
     if weights is not None:
         p.sample_logw, p.sample_mask = _ptr(weights[0]), _ptr(weights[1])
     return p
@@ -415,7 +441,7 @@ def _flash_params(q, k, v, o, lse, causal, scale, flags):
     p.o = _ptr(o)
     p.o_sb, p.o_sh, p.o_sn = _bhn(o)
     p.lse = _ptr(lse)
-    p.status = _ptr(_status_word(q.device))
+    _set_status(p, q.device)
     return p
 
 
@@ -431,7 +457,7 @@ class CausalHyperFunc(torch.autograd.Function):
     merged output."""
 
     @staticmethod
-    def forward(ctx, q, k, v, proj_f32, levels, block_size, sample_size, scale, flags, grad_reference):
+    def forward(ctx, q, k, v, proj_f32, levels, block_size, sample_size, scale, flags, grad_reference, min_seq_len=0):
         _cuda(q, k, v, proj_f32)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         B, H, n, d = q.shape
@@ -445,9 +471,10 @@ class CausalHyperFunc(torch.autograd.Function):
         p.B, p.H, p.n, p.d, p.dv = B, H, n, d, dv
         p.levels, p.block_size, p.sample_size, p.lsh_bits = levels, block_size, sample_size, proj_f32.shape[1]
         p.keep_parts = 1 if (grad_reference and need_grad) else 0
+        p.min_seq_len = min_seq_len
         p.scale = scale
         p.q, p.k, p.v, p.proj, p.o, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(proj_f32), _ptr(o), _ptr(lse)
-        p.status = _ptr(_status_word(dev))
+        _set_status(p, dev)
         lib = L.load()
         saved_bytes = lib.ha_causal_saved_bytes(C.byref(p))
         scratch_bytes = lib.ha_causal_scratch_bytes(C.byref(p), 0)
@@ -460,13 +487,13 @@ class CausalHyperFunc(torch.autograd.Function):
             rc = lib.ha_causal_fwd(C.byref(p), _stream())
         L.check(rc, 'ha_causal_fwd')
         ctx.save_for_backward(q, k, v, o, lse, saved, proj_f32)
-        ctx.cfg = (levels, block_size, sample_size, scale, flags, p.keep_parts)
+        ctx.cfg = (levels, block_size, sample_size, scale, flags, p.keep_parts, min_seq_len)
         return o, lse
 
     @staticmethod
     def backward(ctx, do, dlse_unused=None):
         q, k, v, o, lse, saved, proj_f32 = ctx.saved_tensors
-        levels, block_size, sample_size, scale, flags, keep_parts = ctx.cfg
+        levels, block_size, sample_size, scale, flags, keep_parts, min_seq_len = ctx.cfg
         do = do.contiguous()
         B, H, n, d = q.shape
         dv = v.shape[-1]
@@ -476,10 +503,10 @@ class CausalHyperFunc(torch.autograd.Function):
         p.dtype, p.flags = _dtype_id(q), flags
         p.B, p.H, p.n, p.d, p.dv = B, H, n, d, dv
         p.levels, p.block_size, p.sample_size, p.lsh_bits = levels, block_size, sample_size, proj_f32.shape[1]
-        p.keep_parts, p.scale = keep_parts, scale
+        p.keep_parts, p.scale, p.min_seq_len = keep_parts, scale, min_seq_len
         p.q, p.k, p.v, p.proj, p.o, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(proj_f32), _ptr(o), _ptr(lse)
         p.saved, p.saved_bytes = _ptr(saved), saved.numel()
-        p.status = _ptr(_status_word(dev))
+        _set_status(p, dev)
         lib = L.load()
         scratch_bytes = lib.ha_causal_scratch_bytes(C.byref(p), 1)
         scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=dev)
@@ -488,7 +515,7 @@ class CausalHyperFunc(torch.autograd.Function):
         with torch.cuda.device(dev):
             rc = lib.ha_causal_bwd(C.byref(p), _stream())
         L.check(rc, 'ha_causal_bwd')
-        return dq, dk, dvv, None, None, None, None, None, None, None
+        return dq, dk, dvv, None, None, None, None, None, None, None, None
 
 
 def launch_count():

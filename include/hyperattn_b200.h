@@ -24,7 +24,8 @@ enum {
   HA_ERR_DTYPE = -2,        /* unsupported element type */
   HA_ERR_WORKSPACE = -3,    /* workspace pointer null or too small */
   HA_ERR_CUDA = -4,         /* a CUDA runtime call (launch, attribute) failed; see ha_last_cuda_error */
-  HA_ERR_TOO_LARGE = -5,    /* ha_seg_sort_noalloc: the sort needs more scratch than the built-in array holds */
+  HA_ERR_TOO_LARGE = -5,    /* beyond a size limit of the entry point: a grid dimension (segments, work items), or the
+                               built-in scratch array of ha_seg_sort_noalloc */
   HA_DEV_TIMEOUT = 1        /* a bounded device-side wait gave up (written to the caller's status word) */
 };
 
@@ -144,6 +145,8 @@ typedef struct {
   const float* delta;              /* [B,H,n]: sum_d o*do of the part this call differentiates */
   float *dq_acc, *dk_acc, *dv_acc; /* fp32 [B,H,n,d], [B,H,n,d], [B,H,n,dv] contiguous accumulators (added into) */
   int32_t* status;                 /* optional device status word (0 = ok) */
+  int32_t* status_host;            /* optional word in pinned (device-visible) host memory that gets the same value: the
+                                      host can look at it between calls without synchronising the stream */
   const float* sample_logw;        /* optional [B*H*segs_per_head][m_q/128]: log weight of the kept sampled slots */
   const uint32_t* sample_mask;     /* optional [B*H*segs_per_head][m_q/128][sample_size/32]: bit s = slot s dropped */
   /* backward, HA_MODE_HYPER on the tensor-core kernel only (ha_attn_bwd_uses_tensor_cores): direct dK/dV.  Every key
@@ -199,6 +202,9 @@ int ha_lse_merge(void* o1, float* lse1, const void* o2, const float* lse2, int64
  * for the regular case (n divisible by 2^levels, every rectangle a multiple of 128 rows): hashes q and k once,
  * sorts the segments of every depth, runs the exact leaves and the rectangles deepest first, merging in place.
  * levels = number of half-splits (n / 2^levels <= min_seq_len < n / 2^(levels-1)).
+ * min_seq_len: the module's threshold.  The deepest rectangles have n / 2^levels rows a side; where that is below
+ * min_seq_len the reference computes them exactly (forward_no_causal_mask, hyper_attention.py:109-113), and so does
+ * this call (HA_MODE_FLASH without mask, merged like the others).  0 = every rectangle takes the hyper pattern.
  * saved: workspace that the matching backward call needs again (sort indices of every depth, per-part outputs
  * when keep_parts != 0); scratch: workspace free after the call returns.
  */
@@ -206,6 +212,7 @@ typedef struct {
   int32_t dtype, flags;            /* flags: HA_FLAG_SMOOTH, HA_FLAG_MERGE_EXACT, HA_FLAG_BWD_REF_SMOOTH, HA_FLAG_FORCE_SIMT */
   int32_t B, H, n, d, dv;
   int32_t levels, block_size, sample_size, lsh_bits, keep_parts;
+  int32_t min_seq_len;
   float scale;
   const void *q, *k, *v;           /* [B,H,n,*] contiguous */
   const float* proj;               /* [d][lsh_bits] */
@@ -217,12 +224,19 @@ typedef struct {
   const void* d_o;                 /* [B,H,n,dv] contiguous */
   void *dq, *dk, *dv_out;          /* [B,H,n,*] contiguous, dtype */
   int32_t* status;
+  int32_t* status_host;            /* as in ha_attn_params */
 } ha_causal_params;
 
 int64_t ha_causal_saved_bytes(const ha_causal_params* p);
 int64_t ha_causal_scratch_bytes(const ha_causal_params* p, int32_t backward);
 int ha_causal_fwd(const ha_causal_params* p, void* stream);
 int ha_causal_bwd(const ha_causal_params* p, void* stream);
+
+/* Diagnostic for the timeout path.  One warp polls an mbarrier that nothing ever arrives at, `polls` times (1..2^18),
+ * gives up and reports HA_DEV_TIMEOUT through status / status_host exactly as the attention kernels do when one of their
+ * bounded waits runs out.  No copy and no tensor-core operation is in flight; the kernel returns normally and the
+ * context stays usable.  No counterpart in the reference (its Triton kernels have no waits to bound). */
+int ha_wait_probe(int32_t* status, int32_t* status_host, int32_t polls, void* stream);
 
 /* Number of kernels this library has launched in the calling process (all entry points, all streams). */
 int64_t ha_launch_count(void);

@@ -39,6 +39,17 @@ def test_host_stream_matches_device_call(causal):
         assert torch.equal(o2, o_ref.detach().cpu())
         for g, w in zip((dq, dk, dv), g_ref):                              # fp32 atomics: order-dependent rounding
             assert rel(g, w) < 2e-3
+    # batch of two: a chunk of heads is not contiguous in host memory then (copied per batch index)
+    host2 = [torch.randn(2, 4, n, d).bfloat16().pin_memory() for _ in range(4)]
+    q2, k2, v2, do2 = [t.cuda() for t in host2]
+    q2, k2, v2 = [t.requires_grad_() for t in (q2, k2, v2)]
+    o2_ref = mod(q2, k2, v2, causal=causal)
+    g2_ref = torch.autograd.grad(o2_ref, (q2, k2, v2), do2)
+    res2 = HostStream(mod, heads_per_chunk=3).forward_backward(*host2, causal=causal)
+    check_after()
+    assert torch.equal(res2[0], o2_ref.detach().cpu())
+    for g, w in zip(res2[1:], g2_ref):
+        assert rel(g, w) < 2e-3
     # caller-supplied output buffers, called twice in a row (buffers and streams are reused)
     outs = tuple(torch.empty(B, H, n, d, dtype=torch.bfloat16).pin_memory() for _ in range(4))
     hs = HostStream(mod, heads_per_chunk=2)
