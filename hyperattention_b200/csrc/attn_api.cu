@@ -10,6 +10,9 @@ bool ws_fwd_supported(const ha_attn_params& p);
 bool tc_supported(const ha_attn_params& p);
 bool tc_bwd_supported(const ha_attn_params& p);
 int tc_attn_bwd(const ha_attn_params& p, cudaStream_t st);
+int ws_attn_bwd(const ha_attn_params& p, cudaStream_t st);
+bool ws_bwd_supported(const ha_attn_params& p);
+bool ws_bwd_shape_ok(const ha_attn_params& p);
 
 static int check_common(const ha_attn_params& p, bool backward) {
   if (p.dtype != HA_BF16 && p.dtype != HA_FP16 && p.dtype != HA_FP32) return HA_ERR_DTYPE;
@@ -117,6 +120,7 @@ int ha_attn_bwd(const ha_attn_params* p, void* stream) {
     // one work item must own a key tile's whole dK/dV: exact attention with a single chunk of query tiles
     if (p->mode != HA_MODE_FLASH || p->m_q > 16 * TILE || p->dk_out) return HA_ERR_INVALID;
   }
+  if (!(p->flags & HA_FLAG_FORCE_SIMT) && ws_bwd_supported(*p)) return ws_attn_bwd(*p, st);
   if (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(*p)) return tc_attn_bwd(*p, st);
   if (p->dk_out || (p->flags & HA_FLAG_BWD_KV_INIT)) return HA_ERR_INVALID;   // tensor-core kernel only
   return simt_attn_bwd(*p, st);
@@ -125,6 +129,7 @@ int ha_attn_bwd(const ha_attn_params* p, void* stream) {
 int ha_attn_bwd_direct_level(const ha_attn_params* p) {
   if (!p || !p->d_o || p->mode != HA_MODE_HYPER) return 0;
   if ((p->flags & HA_FLAG_FORCE_SIMT) || !tc_bwd_supported(*p)) return 0;
+  if (ws_bwd_shape_ok(*p)) return 2;   // the warp-specialised kernel sums every query tile's dQ inside one work item
   const bool whole_blocks = !(p->flags & HA_FLAG_SMOOTH) && (p->block_size + TILE - 1) / TILE == 2 && p->m_k % (2 * TILE) == 0;
   if (p->d == 64 && p->dv == 64 && whole_blocks && (p->sample_size == 0 || p->sample_size == 2 * TILE)) return 2;
   return 1;

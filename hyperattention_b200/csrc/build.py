@@ -13,7 +13,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 ROOT = os.path.dirname(PKG)
-SOURCES = ['stream_kernels.cu', 'seg_sort.cu', 'attn_simt.cu', 'attn_tc_fwd.cu', 'attn_tc_fwd_ws.cu', 'attn_tc_bwd.cu', 'attn_api.cu', 'causal.cu']
+SOURCES = ['stream_kernels.cu', 'seg_sort.cu', 'attn_simt.cu', 'attn_tc_fwd.cu', 'attn_tc_fwd_ws.cu', 'attn_tc_bwd.cu', 'attn_tc_bwd_ws.cu', 'attn_api.cu', 'causal.cu']
 LIB = os.path.join(PKG, 'libhyperattn_b200.so')
 NVCC_FLAGS = ['-gencode', 'arch=compute_100a,code=sm_100a', '-O3', '-std=c++17', '-lineinfo', '-Xcompiler', '-fPIC',
               '-I' + os.path.join(ROOT, 'include'), '-I' + HERE]

@@ -339,7 +339,7 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
     if (rc != HA_OK) return rc;
     const bool exact = deepest_exact(p, pl) && l == p.levels - 1;
     a.mode = exact ? HA_MODE_FLASH : HA_MODE_HYPER;
-    a.flags = exact ? (p.flags & HA_FLAG_FORCE_SIMT) : (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_BWD_REF_SMOOTH | HA_FLAG_FORCE_SIMT));
+    a.flags = exact ? (p.flags & HA_FLAG_FORCE_SIMT) : (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_BWD_REF_SMOOTH | HA_FLAG_FORCE_SIMT | HA_FLAG_NO_WS));
     a.segs_per_head = 1 << l;
     a.span = span; a.q_off = m; a.k_off = 0; a.m_q = m; a.m_k = m;
     a.q_idx = exact ? nullptr : sv.q_idx(l); a.k_idx = exact ? nullptr : sv.k_idx(l); a.sample_idx = nullptr;

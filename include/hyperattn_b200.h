@@ -45,7 +45,8 @@ enum {
   HA_FLAG_MERGE_EXACT = 8,   /* with MERGE: plain log-sum-exp combine instead of the reference's rounded formula */
   HA_FLAG_BWD_REF_SMOOTH = 16,/* backward + SMOOTH: enumerate pairs per key tile as the reference backward does */
   HA_FLAG_FORCE_SIMT = 32,   /* use the fp32 CUDA-core kernels even where a tensor-core kernel exists */
-  HA_FLAG_NO_WS = 128,       /* forward: keep the one-tile-per-CTA kernel where the persistent warp-specialised one applies */
+  HA_FLAG_NO_WS = 128,       /* keep the earlier kernels (forward: one tile per CTA; backward: one thread-block role) where the
+                                persistent warp-specialised ones apply */
   HA_FLAG_BWD_KV_INIT = 64   /* backward, HA_MODE_FLASH with m_q <= 2048 on the tensor-core kernel: dk_acc / dv_acc hold
                                 garbage; the launch stores (not adds) every key row of every segment */
 };
@@ -209,7 +210,7 @@ int ha_lse_merge(void* o1, float* lse1, const void* o2, const float* lse2, int64
  * when keep_parts != 0); scratch: workspace free after the call returns.
  */
 typedef struct {
-  int32_t dtype, flags;            /* flags: HA_FLAG_SMOOTH, HA_FLAG_MERGE_EXACT, HA_FLAG_BWD_REF_SMOOTH, HA_FLAG_FORCE_SIMT */
+  int32_t dtype, flags;            /* flags: HA_FLAG_SMOOTH, HA_FLAG_MERGE_EXACT, HA_FLAG_BWD_REF_SMOOTH, HA_FLAG_FORCE_SIMT, HA_FLAG_NO_WS */
   int32_t B, H, n, d, dv;
   int32_t levels, block_size, sample_size, lsh_bits, keep_parts;
   int32_t min_seq_len;
