@@ -110,19 +110,33 @@ class ClockSampler:
         return {'sm_mhz': sm[len(sm) // 2] if sm else None, 'sm_max_mhz': mx, 'reasons': sorted(reasons), 'samples': len(sm)}
 
 
-def timed(fn, steps, warmup, sync_all):
-    """warmup untimed calls, then `steps` calls between CUDA events on the current stream; returns ms per step."""
+def timed(fn, steps, warmup, sync_all, stats=None):
+    """warmup untimed calls, then `steps` calls between CUDA events on the current stream; returns ms per step (total
+    time of the K steps / K).  With stats (a dict): an event after every step as well, from which the median and the 0.2 /
+    0.8 quantiles of the per-step times are taken (the reference's protocol, benchmark_single_attention.py:40-52); if fn
+    returns a CUDA event recorded inside the step (end of its forward), the forward and backward shares too."""
     for _ in range(warmup):
         fn()
     sync_all()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        fn()
-    e1.record()
-    e1.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    mids = []
+    ev[0].record()
+    for i in range(steps):
+        m = fn()
+        if stats is not None and isinstance(m, torch.cuda.Event):
+            mids.append(m)
+        ev[i + 1].record()
+    ev[-1].synchronize()
     sync_all()
-    return e0.elapsed_time(e1) / steps
+    if stats is not None:
+        per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(steps))
+        q = lambda f: per[min(steps - 1, int(f * steps))]
+        stats.update({'median_ms': q(0.5), 'q20_ms': q(0.2), 'q80_ms': q(0.8), 'reps': steps})
+        if len(mids) == steps:
+            f = sorted(ev[i].elapsed_time(mids[i]) for i in range(steps))
+            b = sorted(mids[i].elapsed_time(ev[i + 1]) for i in range(steps))
+            stats.update({'fwd_median_ms': f[steps // 2], 'bwd_median_ms': b[steps // 2]})
+    return ev[0].elapsed_time(ev[-1]) / steps
 
 
 def cpu_baseline(workload, n, d, heads_sample, total_heads, seed, target_seconds=12.0):
@@ -228,7 +242,10 @@ def main():
 
     def fwd_bwd():
         o = mod(q, k, v, causal=causal)
-        return torch.autograd.grad(o, (q, k, v), do)
+        mid = torch.cuda.Event(enable_timing=True)
+        mid.record()
+        torch.autograd.grad(o, (q, k, v), do)
+        return mid
 
     sampler = ClockSampler(torch.cuda.current_device() if 'CUDA_VISIBLE_DEVICES' not in os.environ else local_rank)
     launches0 = ha.launch_count()
@@ -236,13 +253,37 @@ def main():
     sync_all()
     sampler.start()
     l0 = ha.launch_count()
-    ms = timed(fwd_bwd, args.steps, args.warmup, sync_all)
+    step_stats = {}
+    ms = timed(fwd_bwd, args.steps, args.warmup, sync_all, step_stats)
     launches = (ha.launch_count() - l0) // (args.steps + args.warmup) * args.steps
     ms_fwd = timed(fwd, args.steps, args.warmup, sync_all)
+    # host time to enqueue one step without waiting for the device (what bounds the step when a rank owns few heads)
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(5):
+        fwd_bwd()
+    host_enqueue_ms = (time.perf_counter() - t0) / 5 * 1e3
+    sync_all()
+    # the causal configuration (benchmark configuration 2) on the same tensors and the same ranks: times do not depend on the values
+    def c_fwd():
+        with torch.no_grad():
+            return mod(q, k, v, causal=True)
+    def c_fwd_bwd():
+        oo = mod(q, k, v, causal=True)
+        mid = torch.cuda.Event(enable_timing=True)
+        mid.record()
+        torch.autograd.grad(oo, (q, k, v), do)
+        return mid
+    c_stats = {}
+    c_steps = max(3, args.steps // 2)
+    c_fwd_bwd()
+    tc_fb = timed(c_fwd_bwd, c_steps, 2, sync_all, c_stats)
+    tc_f = timed(c_fwd, c_steps, 2, sync_all)
     if dist is not None:
-        t = torch.tensor([ms, ms_fwd], device=dev)
+        t = torch.tensor([ms, ms_fwd, tc_fb, tc_f, host_enqueue_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, ms_fwd = t.tolist()
+        ms, ms_fwd, tc_fb, tc_f, host_enqueue_ms = t.tolist()
+    causal2 = {'fwd_ms': tc_f, 'fwd_bwd_ms': tc_fb, 'fwd_bwd_tokens_per_s': n / (tc_fb * 1e-3), 'steps': c_steps, 'timing': 'max over ranks', **c_stats}
 
     # end to end through the public host-buffer API: pinned H2D of q, k, v, do and D2H of o and the three gradients every
     # step, streamed over chunks of heads (copy-in, kernels and copy-out overlap; PCIe is full duplex)
@@ -251,7 +292,7 @@ def main():
     hs = HostStream(mod)
     def e2e_step():
         hs.forward_backward(*host, causal=causal, out=outs)
-    ms_e2e = timed(e2e_step, max(2, args.steps // 2), 2, sync_all)
+    ms_e2e = timed(e2e_step, args.steps, args.warmup, sync_all)
     if dist is not None:
         t = torch.tensor([ms_e2e], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -263,13 +304,14 @@ def main():
     line = {'metric': 'hyperattention_fwd_bwd_tokens_per_s', 'value': n / (ms * 1e-3), 'unit': 'tokens/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic', 'config': config, 'fwd_ms': ms_fwd, 'fwd_tokens_per_s': n / (ms_fwd * 1e-3),
-            'clocks': clocks, 'gpu_launches': int(launches),
+            'clocks': clocks, 'gpu_launches': int(launches), 'step_stats': step_stats, 'host_enqueue_ms': host_enqueue_ms,
+            'causal_config2': causal2,
             'e2e': {'value': n / (ms_e2e * 1e-3), 'unit': 'tokens/s', 'ms_per_step': ms_e2e, 'h2d_bytes_per_step': bytes_io,
                     'd2h_bytes_per_step': bytes_io, 'api': 'hyperattention_b200.host.HostStream.forward_backward',
                     'pcie_gbs_each_way': bytes_io / (ms_e2e * 1e-3) / 1e9}}
 
     if rank == 0 and not args.no_extras:
-        line.update(extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev))
+        line.update(extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev, tc_f, tc_fb))
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:
@@ -277,14 +319,19 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM traffic of the dominant kernel (attn_tc_bwd_kernel, hyper pattern: one launch per backward, fused block + sampled
-# work items), from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of the 8-head x 65536-token case, which
-# scales linearly with the number of rows (fixed work per row): 278.6 MB read, 161.4 MB written for 524288 rows.
-# Summary of the capture: profiles/attn_tc_bwd_kernel_hyper_8x65536.md.
-BWD_DRAM_BYTES_PER_ROW = 839.0
+def kernel_traffic(kernel, rows):
+    """Measured DRAM traffic of one launch of `kernel` over `rows` rows (dram__bytes_read.sum + dram__bytes_write.sum of an
+    ncu capture on a smaller case, which scales with the rows: fixed work per row), from the tracked table of captures;
+    None when no capture of this kernel is on record."""
+    path = os.path.join(ROOT, 'profiles', 'kernel_dram_traffic.json')
+    try:
+        entry = json.load(open(path))[kernel]
+        return entry['dram_bytes'] / entry['rows'] * rows
+    except (OSError, KeyError, ValueError):
+        return None
 
 
-def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
+def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev, tc_f, tc_fb):
     """Kernel-alone timings and rooflines (CUDA events on the launching stream), the exact-flash comparator, the causal
     configuration's times, the CPU baseline."""
     from hyperattention_b200 import ops
@@ -336,22 +383,11 @@ def extras(args, ha, mod, q, k, v, do, causal, n, d, hpg, heads, seed, dev):
         r_['frac'] = r_['achieved'] / r_['peak']
     out['stage_rooflines'] = st
     ach = tf(fl_bwd, t_bwd)
-    out['roofline'] = {'bound': 'tensor', 'kernel': 'attn_tc_bwd_kernel (hyper pattern, one launch per backward; the longest kernel of the step)', 'achieved': ach,
+    out['roofline'] = {'bound': 'tensor', 'kernel': 'attn_tc_bwd_ws_kernel (hyper pattern, one launch per backward; the longest kernel of the step)', 'achieved': ach,
                        'peak': peaks['bf16_tflops'], 'unit': 'TFLOP/s', 'frac': ach / peaks['bf16_tflops'],
-                       'traffic': BWD_DRAM_BYTES_PER_ROW * rows if BWD_DRAM_BYTES_PER_ROW else None,
+                       'traffic': kernel_traffic('attn_tc_bwd_ws_kernel', rows),
                        'peak_source': peaks['src'], 'launch_ms': t_bwd, 'algorithmic_flops_per_launch': fl_bwd,
                        'algorithmic_bytes_per_launch': rows * (7 * d * 2 + 8)}
-    # the causal configuration (benchmark configuration 2) on the same tensors: times do not depend on the values
-    def c_fwd():
-        with torch.no_grad():
-            return mod(q, k, v, causal=True)
-    def c_fwd_bwd():
-        oo = mod(q, k, v, causal=True)
-        return torch.autograd.grad(oo, (q, k, v), do)
-    c_fwd_bwd()
-    tc_fb = timed(c_fwd_bwd, 5, 2, sync)
-    tc_f = timed(c_fwd, 5, 2, sync)
-    out['causal_config2'] = {'fwd_ms': tc_f, 'fwd_bwd_ms': tc_fb, 'fwd_bwd_tokens_per_s': n / (tc_fb * 1e-3)}
     # the same step with uniformly sampled, importance-weighted key columns (fresh draws every call)
     if not causal:
         umod = ha.HyperAttention(input_dim=d, lsh_num_projs=BITS, block_size=BLOCK, sample_size=SAMPLE, min_seq_len=MIN_SEQ,

@@ -774,11 +774,8 @@ static int launch_bwd(const ha_attn_params& p, cudaStream_t st) {
     items = (long long)n_kt * n_chunks;
   }
   if (items > 0x7fffffffLL) return HA_ERR_INVALID;
-  HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_bwd_kernel<T, D, DV, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
-             "ha_attn_bwd smem attribute");
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  HA_SMEM_ATTR_ONCE((attn_tc_bwd_kernel<T, D, DV, WT>), Cfg::SMEM, "ha_attn_bwd smem attribute");
+  const int sms = sm_count();
   // persistent CTAs, one per SM (512 TMEM columns, > 190 KB shared memory each): CTA c starts with work item c and
   // draws the following ones from a counter, which is one of a small rotating set of device words zeroed in stream
   // order before the launch

@@ -13,17 +13,20 @@
 // of 64 query columns, so that two TMEM stages of (S^T, dP^T) fit beside the accumulators and the elementwise phase of
 // one half runs underneath the tensor work of the other.
 //
-// Roles (512 threads):
-//   * elementwise group g (g = 0, 1; 128 threads, thread = key row = TMEM lane): the halves with query columns
-//     [64 g, 64 g + 64) of every pair, on TMEM stage g.
+// Roles (640 threads):
+//   * elementwise groups g = 0, 1 (128 threads each, thread = key row = TMEM lane): query columns [32 g, 32 g + 32) of
+//     every half.  Both groups work on the same half, so a half's elementwise phase is short and the other TMEM stage
+//     is in its tensor phases meanwhile.
 //   * drain group (128 threads, thread = TMEM lane): dK / dV rows of a finished key tile, dQ rows of a finished query
 //     tile -> global memory (typed rows, or fp32 reductions into accumulators / slot buffers).
 //   * loader warp: gathers rows by index with cp.async into two K/V stages and two (Q, dO, lse, delta) stages; the
 //     copies signal the "full" barriers themselves, the warp only waits for free buffers and runs ahead.
-//   * three MMA-issuing threads (one per warp): S^T / dP^T of every half; dV / dK of every half as soon as its P^T / dS^T
-//     are written; dQ of every pair.  Every completion is a tcgen05.commit onto an mbarrier.
-// TMEM columns: stage g at 128 g (S^T 64 columns, dP^T 64 columns; P^T / dS^T in place over the first 32 of each),
-// dV 256, dK 320, dQ of query tile 0 / 1 at 384 / 448.
+//   * five MMA-issuing threads (one per warp), one product each: S^T, dP^T, dV, dK of every half, dQ of every pair.
+//     One thread gets a tcgen05.mma accepted only about every 100 cycles, whatever its shape, while the tensor pipe
+//     finishes an M 128 x N 64 x K 16 step in under 60 (measured); five issuers keep the pipe fed and keep the 4-instruction
+//     products on the stage's critical path short.  Every completion is a tcgen05.commit onto an mbarrier.
+// TMEM columns: stage s at 128 s: S^T in [0, 64), dP^T in [64, 128); group g writes P^T / dS^T (16 packed columns) in place
+// over the first half of the 32 columns it has read.  dV 256, dK 320, dQ of query tile 0 / 1 at 384 / 448.
 // Hand-offs are mbarriers with bounded waits; a wait that gives up raises the CTA's abort flag and the status words,
 // and every role leaves its loop at its next wait.
 #include "attn_index.cuh"
@@ -36,16 +39,51 @@ namespace ha {
 namespace bws {
 constexpr int D = 64, DV = 64;
 constexpr int TILE_B = TILE * 64 * 2;                          // one 128 x 64 tile of 2-byte elements
-constexpr int OFF_KV = 0;                                      // stage s: K at s * 2 TILE_B, V after it
-constexpr int OFF_QD = OFF_KV + 2 * 2 * TILE_B;                // stage y (query tile y of the item): Q, then dO
+constexpr int K_STAGES = 3, V_STAGES = 2;                      // dQ reads K a pair or two after S^T has: K gets the deeper ring
+constexpr int OFF_K = 0;                                       // K ring
+constexpr int OFF_V = OFF_K + K_STAGES * TILE_B;               // V ring
+constexpr int OFF_QD = OFF_V + V_STAGES * TILE_B;              // stage y (query tile y of the item): Q, then dO
 constexpr int OFF_DS = OFF_QD + 2 * 2 * TILE_B;                // two buffers (pairs alternate) of two slabs (column halves)
 constexpr int OFF_LD = OFF_DS + 2 * 2 * TILE_B;                // per query-tile stage: lse[128], delta[128] (fp32)
 constexpr int SMEM = OFF_LD + 2 * 1024 + 1024;                 // + alignment slack
-constexpr int THREADS = 512;
+constexpr int THREADS = 640;
 constexpr int COL_DV = 256, COL_DK = 320, COL_DQ = 384;
-// barrier slots
-constexpr int B_KV_FULL = 0, B_KV_EMPTY = 2, B_QD_FULL = 4, B_QD_EMPTY = 6, B_S_READY = 8, B_P_READY = 10, B_ST_FREE = 12,
-              B_DS_FREE = 14, B_DQ_FULL = 16, B_DQ_FREE = 18, B_ACC_FULL = 20, B_ACC_FREE = 21, N_BARS = 22;
+// barrier slots (index + stage / buffer / query tile) and their arrivals per phase
+enum {
+  B_K_FULL = 0,      // 3 x 32: every loader lane, through its copies
+  B_K_EMPTY = 3,     // 3 x 2: the S^T and dQ issuers
+  B_V_FULL = 6,      // 2 x 32
+  B_V_EMPTY = 8,     // 2 x 1: the dP^T issuer
+  B_QD_FULL = 10,    // 2 x 32
+  B_QD_EMPTY = 12,   // 2 x 4: the S^T, dP^T, dV and dK issuers
+  B_S_READY = 14,    // 2 x 2: S^T and dP^T of a half are in TMEM
+  B_P_READY = 16,    // 2 x 256: both elementwise groups have written P^T / dS^T of the half
+  B_SF_S = 18,       // 2 x 1: dV of the stage's half completed: its S^T columns may be overwritten
+  B_SF_P = 20,       // 2 x 1: dK ...: its dP^T columns
+  B_DS_FREE = 22,    // 2 x 1: dQ of the pair has read the dS buffer
+  B_DQ_FULL = 24,    // 2 x 1: dQ of a query tile complete
+  B_DQ_FREE = 26,    // 2 x 128: ... drained
+  B_LDT = 28,        // 2 x 256: lse / delta of a query tile pre-scaled by the elementwise threads
+  B_DS_FULL = 30,    // 2 x 512: both halves' dS slabs of a pair are in the buffer (every elementwise thread, twice)
+  B_ACC_FULL = 32,   // 2: dV and dK of a key tile complete
+  B_ACC_FREE = 33,   // 128: ... drained
+  N_BARS = 34
+};
+__device__ __forceinline__ int bar_count(int i) {
+  if (i < B_K_EMPTY) return 32;
+  if (i < B_V_FULL) return 2;
+  if (i < B_V_EMPTY) return 32;
+  if (i < B_QD_FULL) return 1;
+  if (i < B_QD_EMPTY) return 32;
+  if (i < B_S_READY) return 4;
+  if (i < B_P_READY) return 2;
+  if (i < B_SF_S) return 256;
+  if (i < B_DQ_FREE) return 1;          // stage-free (S, P), dS-free, dQ-full
+  if (i < B_LDT) return 128;
+  if (i < B_DS_FULL) return 256;
+  if (i < B_ACC_FULL) return 512;
+  return i == B_ACC_FULL ? 2 : 128;
+}
 }  // namespace bws
 
 // 128 rows x 64 elements gathered by ONE warp: rows[q] = source row of tile row 32 q + lane (-1: zero fill)
@@ -91,15 +129,7 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
   if (cta_sees_failure(p.status, &s_bail)) return;   // an earlier CTA gave up: drain quickly (uniform over the CTA)
   auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
   if (tid == 0) {
-    // arrivals per phase: 32 (every loader lane, through its copies) on the "full" barriers of the operand stages, 128 (a
-    // thread group) on P-ready / dQ-free / accumulator-free, 1 or 2 (tcgen05.commit) elsewhere
-    for (int i = 0; i < N_BARS; ++i) {
-      const bool by_loader = (i >= B_KV_FULL && i < B_KV_FULL + 2) || (i >= B_QD_FULL && i < B_QD_FULL + 2);
-      const bool by_group = (i >= B_P_READY && i < B_P_READY + 2) || (i >= B_DQ_FREE && i < B_DQ_FREE + 2) || i == B_ACC_FREE;
-      // the "empty" barriers of the operand stages: one commit from each of the two MMA-issuing threads that read the stage
-      const bool by_two = (i >= B_KV_EMPTY && i < B_KV_EMPTY + 2) || (i >= B_QD_EMPTY && i < B_QD_EMPTY + 2);
-      mbar_init(bar(i), by_loader ? 32 : by_group ? 128 : by_two ? 2 : 1);
-    }
+    for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), bar_count(i));
     s_abort = 0;
     mbar_fence_init();
   }
@@ -122,70 +152,82 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
     // =====================================================================================================
     // elementwise groups: P^T = exp2(S^T scale log2e - lse log2e), dS^T = P^T (dP^T - delta) scale
     // =====================================================================================================
-    // Register budget: 512 threads x 128 at launch = the whole register file.  The drain group goes down to 96 and the
-    // loader / MMA warpgroup to 72, the two elementwise groups take 168: 2 x 128 x 168 + 128 x 96 + 128 x 72 = 64512 of
-    // 65536, i.e. with slack -- a request that the pool cannot satisfy would wait forever.
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 168;");
+    // Register budget.  What setmaxnreg redistributes is the CTA's own allocation at launch: 640 threads x 96 registers =
+    // 61440 (not the SM's whole file); a request beyond it waits forever.  The two elementwise groups go up to 120, the
+    // drain group to 112 (it holds two packed accumulator rows), the two warpgroups of the loader and the MMA issuers go
+    // down to 64: 2 x 128 x 120 + 128 x 112 + 2 x 128 x 64 = 61440.
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
     const int g = warp >> 2, gw = warp & 3, row = tid & 127;
     const uint32_t lane_sel = (uint32_t)(gw * 32) << 16;
-    const uint32_t tST = tmem + 128 * g + lane_sel, tDPT = tST + 64;
-    const uint64_t sc2 = pack_f2(p.scale * LOG2E, p.scale * LOG2E), nl2e = pack_f2(-LOG2E, -LOG2E);
-    const uint64_t scl = pack_f2(p.scale, p.scale), nscl = pack_f2(-p.scale, -p.scale);
-    uint32_t pairs = 0;      // pairs this group has processed (stage g is used once per pair)
+    const uint64_t sc2 = pack_f2(p.scale * LOG2E, p.scale * LOG2E), scl = pack_f2(p.scale, p.scale);
+    uint32_t hh = 0;         // halves processed (pair = hh / 2, TMEM stage = dS slab = hh & 1)
     bool ok = true;
     int it = 0;
     HA_T_DECL(8)
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
-      for (int x = 0; x < nX && ok; ++x) {
-        for (int y = 0; y < 2 && ok; ++y, ++pairs) {
+      for (int xy = 0; xy < 2 * nX && ok; ++xy) {
+        const int x = xy >> 1, y = xy & 1;
+        for (int s = 0; s < 2 && ok; ++s, ++hh) {
+          const uint32_t pair = hh >> 1;
           HA_T_MARK(4)
-          if (!(ok = wait(B_S_READY + g, pairs & 1))) break;
+          if (!(ok = wait(B_S_READY + s, pair & 1))) break;
           HA_T_MARK(0)
-          if (x == 0 && !(ok = wait(B_QD_FULL + y, it & 1))) break;                    // lse / delta of the tile have landed
+          float* ldt = reinterpret_cast<float*>(smem + OFF_LD + y * 1024);
+          if (x == 0 && s == 0) {
+            // lse / delta of the query tile have landed: scale them once for all of the item's pairs (256 values, one per
+            // elementwise thread), then meet on a barrier of their own
+            if (!(ok = wait(B_QD_FULL + y, it & 1))) break;
+            ldt[tid] *= tid < TILE ? -LOG2E : -p.scale;
+            mbar_arrive(bar(B_LDT + y));
+            if (!(ok = wait(B_LDT + y, it & 1))) break;
+          }
           HA_T_MARK(1)
-          if (pairs >= 2 && !(ok = wait(B_DS_FREE + (pairs & 1), ((pairs >> 1) - 1) & 1))) break;   // dQ of pair - 2 has read the buffer
+          if (pair >= 2 && !(ok = wait(B_DS_FREE + (pair & 1), ((pair >> 1) - 1) & 1))) break;   // dQ of pair - 2 has read the buffer
           HA_T_MARK(2)
           tc_fence_after();
-          const float* ld = reinterpret_cast<const float*>(smem + OFF_LD + y * 1024) + 64 * g;
-          uint8_t* ds_row = smem + OFF_DS + (pairs & 1) * 2 * TILE_B + g * TILE_B + row * 128;
+          // this thread: key row `row`, query columns 64 s + 32 g + [0, 32) of the pair
+          const uint32_t tS = tmem + 128 * s + 32 * g + lane_sel, tDP = tS + 64;
+          const float* ld = ldt + 64 * s + 32 * g;
+          uint8_t* ds_row = smem + OFF_DS + (pair & 1) * 2 * TILE_B + s * TILE_B + row * 128;
+          uint32_t rs[32], rp[32];
+          tmem_ld32(tS, rs);
+          tmem_ld32(tDP, rp);
+          tmem_ld_fence(rs);
+          tmem_ld_fence(rp);
+          uint32_t pk[16], dk[16];
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t rs[32], rp[32];
-            tmem_ld32(tST + c * 32, rs);
-            tmem_ld32(tDPT + c * 32, rp);
-            tmem_ld_fence(rs);
-            tmem_ld_fence(rp);
-            uint32_t pk[16], dk[16];
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              // four query columns: their lse and delta (the same for every thread: broadcast reads)
-              const ulonglong2 L = *reinterpret_cast<const ulonglong2*>(ld + c * 32 + i);
-              const ulonglong2 Dl = *reinterpret_cast<const ulonglong2*>(ld + 128 + c * 32 + i);
-              float p0, p1, p2, p3, d0, d1, d2, d3;
-              unpack_f2(ffma2(pack_u2(rs[i], rs[i + 1]), sc2, fmul2(L.x, nl2e)), p0, p1);
-              unpack_f2(ffma2(pack_u2(rs[i + 2], rs[i + 3]), sc2, fmul2(L.y, nl2e)), p2, p3);
-              p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
-              // ds = p * (dp - delta) * scale
-              unpack_f2(fmul2(pack_f2(p0, p1), ffma2(pack_u2(rp[i], rp[i + 1]), scl, fmul2(Dl.x, nscl))), d0, d1);
-              unpack_f2(fmul2(pack_f2(p2, p3), ffma2(pack_u2(rp[i + 2], rp[i + 3]), scl, fmul2(Dl.y, nscl))), d2, d3);
-              pk[i >> 1] = pack2<T>(p0, p1);
-              pk[(i >> 1) + 1] = pack2<T>(p2, p3);
-              dk[i >> 1] = pack2<T>(d0, d1);
-              dk[(i >> 1) + 1] = pack2<T>(d2, d3);
-            }
-            // P^T / dS^T chunk c overwrite columns [16 c, 16 c + 16) of S^T / dP^T: part of chunk 0, which is in registers
-            tmem_st16(tST + c * 16, pk);
-            tmem_st16(tDPT + c * 16, dk);
-            // dS^T rows to shared memory: this key row, query columns 64 g + 32 c + [0, 32) = 16-byte chunks 4 c .. 4 c + 3
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<uint4*>(ds_row + ((((c * 4 + j) ^ row) & 7) << 4)) = make_uint4(dk[4 * j], dk[4 * j + 1], dk[4 * j + 2], dk[4 * j + 3]);
+          for (int i = 0; i < 32; i += 4) {
+            // four query columns: their (scaled) lse and delta, the same for every thread: broadcast reads
+            const ulonglong2 L = *reinterpret_cast<const ulonglong2*>(ld + i);
+            const ulonglong2 Dl = *reinterpret_cast<const ulonglong2*>(ld + TILE + i);
+            float p0, p1, p2, p3, d0, d1, d2, d3;
+            unpack_f2(ffma2(pack_u2(rs[i], rs[i + 1]), sc2, L.x), p0, p1);
+            unpack_f2(ffma2(pack_u2(rs[i + 2], rs[i + 3]), sc2, L.y), p2, p3);
+            p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
+            // ds = p * (dp - delta) * scale
+            unpack_f2(fmul2(pack_f2(p0, p1), ffma2(pack_u2(rp[i], rp[i + 1]), scl, Dl.x)), d0, d1);
+            unpack_f2(fmul2(pack_f2(p2, p3), ffma2(pack_u2(rp[i + 2], rp[i + 3]), scl, Dl.y)), d2, d3);
+            pk[i >> 1] = pack2<T>(p0, p1);
+            pk[(i >> 1) + 1] = pack2<T>(p2, p3);
+            dk[i >> 1] = pack2<T>(d0, d1);
+            dk[(i >> 1) + 1] = pack2<T>(d2, d3);
           }
+          // P^T / dS^T (16 packed columns) over the first half of the 32 columns this thread has just read
+          tmem_st16(tS, pk);
+          tmem_st16(tDP, dk);
+          // dS^T row to shared memory: slab s, this key row, 16-byte chunks 4 g .. 4 g + 3
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(ds_row + ((((g * 4 + j) ^ row) & 7) << 4)) = make_uint4(dk[4 * j], dk[4 * j + 1], dk[4 * j + 2], dk[4 * j + 3]);
           HA_T_MARK(3)
           tmem_st_wait();
           fence_async_smem();       // the dS rows are read by the tensor core (async proxy)
           tc_fence_before();
-          mbar_arrive(bar(B_P_READY + g));
+          mbar_arrive(bar(B_P_READY + s));
+          // The dQ issuer follows the dS buffers, not the TMEM stages: it may run up to two pairs behind this thread, and a
+          // parity wait must never fall two phases behind its barrier; the buffer's own barrier cannot run ahead of it,
+          // because the buffer is not rewritten before its dQ has completed.
+          mbar_arrive(bar(B_DS_FULL + (pair & 1)));
         }
       }
     }
@@ -194,33 +236,38 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
     // =====================================================================================================
     // drain group: finished accumulators -> global memory
     // =====================================================================================================
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 96;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
     const int gw = warp & 3, row = tid & 127;
     const uint32_t lane_sel = (uint32_t)(gw * 32) << 16;
     bool ok = true;
     int it = 0;
     uint32_t xg = 0;         // key tiles drained so far
     HA_T_DECL(8)
-    // 32 fp32 columns of this lane -> 32 typed elements at dst (64 contiguous bytes), or fp32 reductions at acc
-    auto out_chunk = [&](uint32_t taddr, T* dst, float* acc, bool typed, bool valid, bool last, int free_bar) {
-      uint32_t r[32];
-      tmem_ld32(taddr, r);
-      tmem_ld_fence(r);
-      if (last) {            // everything this thread reads from the accumulator is in registers: hand it back
-        tc_fence_before();
-        mbar_arrive(bar(free_bar));
+    // An accumulator is handed back as early as possible: its 64 fp32 columns of this lane are read and rounded to the
+    // tensors' dtype in registers (32 packed words), the "free" barrier is signalled, and only then do the words go out --
+    // as one typed row (128 contiguous bytes), or, unpacked again, as fp32 reductions.  (What is added into an fp32
+    // accumulator or slot buffer is therefore rounded per work item, as the typed rows are.)
+    auto grab = [&](uint32_t taddr, uint32_t (&w)[32]) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c * 16, r);
+        tmem_ld_fence16(r);
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) w[c * 8 + (i >> 1)] = pack2<T>(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
       }
-      if (!valid) return;
+    };
+    auto put = [&](const uint32_t (&w)[32], T* dst, float* acc, bool typed) {
       if (typed) {
         uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-        for (int i = 0; i < 32; i += 8)
-          d4[i >> 3] = make_uint4(pack2<T>(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), pack2<T>(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
-                                  pack2<T>(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])), pack2<T>(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+        for (int i = 0; i < 32; i += 4) d4[i >> 2] = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4)
-          bws_red_add_v4(acc + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        for (int i = 0; i < 32; i += 2) {
+          const float2 lo = unpack2<T>(w[i]), hi = unpack2<T>(w[i + 1]);
+          bws_red_add_v4(acc + 2 * i, lo.x, lo.y, hi.x, hi.y);
+        }
       }
     };
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
@@ -241,9 +288,11 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
         HA_T_MARK(2)
         tc_fence_after();
         const long long r = head0 + si.q_row0 + (y ? qrow1 : qrow0);
-        const uint32_t t = tmem + COL_DQ + y * D + lane_sel;
-        out_chunk(t, (T*)p.dq_out + r * D, p.dq_acc + r * D, dq_direct, true, false, 0);
-        out_chunk(t + 32, (T*)p.dq_out + r * D + 32, p.dq_acc + r * D + 32, dq_direct, true, true, B_DQ_FREE + y);
+        uint32_t w[32];
+        grab(tmem + COL_DQ + y * D + lane_sel, w);
+        tc_fence_before();
+        mbar_arrive(bar(B_DQ_FREE + y));
+        put(w, (T*)p.dq_out + r * D, p.dq_acc + r * D, dq_direct);
         HA_T_MARK(3)
         return true;
       };
@@ -270,41 +319,43 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
           acc_k = p.dk_acc + r * D;
           acc_v = p.dv_acc + r * DV;
         }
-        const uint32_t tv = tmem + COL_DV + lane_sel, tk = tmem + COL_DK + lane_sel;
-        out_chunk(tv, (T*)p.dv_out + r * DV, acc_v, typed, true, false, 0);
-        out_chunk(tv + 32, (T*)p.dv_out + r * DV + 32, acc_v + 32, typed, true, false, 0);
-        out_chunk(tk, (T*)p.dk_out + r * D, acc_k, typed, true, false, 0);
-        out_chunk(tk + 32, (T*)p.dk_out + r * D + 32, acc_k + 32, typed, true, true, B_ACC_FREE);
+        {
+          uint32_t wv[32], wk[32];
+          grab(tmem + COL_DV + lane_sel, wv);
+          grab(tmem + COL_DK + lane_sel, wk);
+          tc_fence_before();
+          mbar_arrive(bar(B_ACC_FREE));
+          HA_T_MARK(4)
+          put(wv, (T*)p.dv_out + r * DV, acc_v, typed);
+          put(wk, (T*)p.dk_out + r * D, acc_k, typed);
+        }
         krow = krow_next;
       }
       if (ok) ok = drain_dq(1);
     }
     HA_T_DUMP(8, (int)blockIdx.x * 4 + 2, row == 0)
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
-    if (warp == 12) {
+    // warps 12 .. 19: three loader warps and five MMA-issuing threads (two warpgroups of 64 registers)
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if (warp <= 14) {
       // ===================================================================================================
-      // loader: per item K/V of the first key tile, (Q, dO, lse, delta) of both query tiles, then the other key tiles
+      // loaders, one warp per operand stream: K tiles (warp 12), V tiles (warp 13), (Q, dO, lse, delta) tiles (warp 14).
+      // One warp issuing every gather was the bottleneck of the whole CTA (measured: about 3500 cycles to issue one
+      // tile's copies); the streams are independent -- each has its own ring and its own barriers.
       // ===================================================================================================
       // The copies of a tile signal its barrier themselves when they land (every lane arrives once, through the copy
-      // engine), so this warp never waits for its own copies: only for free buffers.
+      // engine), so a loader never waits for its own copies: only for free buffers.
       auto push = [&](int b) {
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(b)) : "memory");
       };
-      uint32_t xg = 0;        // key tiles fetched so far (stage = xg & 1)
       bool ok = true;
       int it = 0;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
-        const int seg = item / blocks_per_seg, blk = item - seg * blocks_per_seg;
-        const SegInfo si = seg_info(p, seg);
-        const long long head0 = ((long long)(si.b * p.H + si.h)) * p.n;
-        const uint16_t* qbase = (const uint16_t*)p.q + si.b * p.q_sb + si.h * p.q_sh + si.q_row0 * p.q_sn;
-        const uint16_t* gbase = (const uint16_t*)p.d_o + si.b * p.do_sb + si.h * p.do_sh + si.q_row0 * p.do_sn;
-        const uint16_t* kbase = (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
-        const uint16_t* vbase = (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn;
-        const float* lse_base = p.lse + head0 + si.q_row0;
-        const float* delta_base = p.delta + head0 + si.q_row0;
-        auto load_krows = [&](int x, int (&dst)[4]) {
+      HA_T_DECL(8)
+      if (warp <= 13) {
+        const bool is_v = warp == 13;
+        const int n_st = is_v ? V_STAGES : K_STAGES;
+        uint32_t xg = 0;        // key tiles fetched so far
+        auto load_krows = [&](int seg, int blk, int x, int (&dst)[4]) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int rr = q * 32 + lane;
@@ -315,132 +366,173 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
             }
           }
         };
-        int krows[4];
-        load_krows(0, krows);
-        for (int x = 0; x < nX && ok; ++x, ++xg) {
-          const int stage = xg & 1;
-          int knext[4] = {-1, -1, -1, -1};
-          if (x + 1 < nX) load_krows(x + 1, knext);
-          int qrows[2][4];
-          if (x == 0) {
+        int krows[4] = {-1, -1, -1, -1};
+        if ((int)blockIdx.x < n_items) load_krows(blockIdx.x / blocks_per_seg, blockIdx.x % blocks_per_seg, 0, krows);
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+          const int seg = item / blocks_per_seg, blk = item - seg * blocks_per_seg;
+          const SegInfo si = seg_info(p, seg);
+          const uint16_t* base = is_v ? (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn
+                                      : (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
+          const int64_t sn = is_v ? p.v_sn : p.k_sn;
+          for (int x = 0; x < nX && ok; ++x, ++xg) {
+            // the next tile's row indices (the next item's first tile after this item's last) travel during the wait
+            int knext[4] = {-1, -1, -1, -1};
+            if (x + 1 < nX) load_krows(seg, blk, x + 1, knext);
+            else if (item + (int)gridDim.x < n_items) load_krows((item + gridDim.x) / blocks_per_seg, (item + gridDim.x) % blocks_per_seg, 0, knext);
+            // ... and its rows are pulled into L2 (one 128-byte line each), so that the copies below, whose number in flight
+            // is limited, meet L2 latency rather than DRAM latency
+            if (x + 1 < 2 || x + 1 == nX) {       // window tiles only: the sampled rows are shared by the whole segment
+              const SegInfo nsi = x + 1 < nX ? si : seg_info(p, (item + (int)gridDim.x) / blocks_per_seg);
+              const uint16_t* nbase = is_v ? (const uint16_t*)p.v + nsi.b * p.v_sb + nsi.h * p.v_sh + nsi.k_row0 * p.v_sn
+                                           : (const uint16_t*)p.k + nsi.b * p.k_sb + nsi.h * p.k_sh + nsi.k_row0 * p.k_sn;
 #pragma unroll
-            for (int y = 0; y < 2; ++y)
+              for (int q = 0; q < 4; ++q)
+                if (knext[q] >= 0) prefetch_l2(nbase + (int64_t)knext[q] * sn);
+            }
+            const int st = xg % n_st;
+            HA_T_MARK(0)
+            if (xg >= (uint32_t)n_st && !(ok = wait((is_v ? B_V_EMPTY : B_K_EMPTY) + st, (xg / n_st - 1) & 1))) break;
+            HA_T_MARK(1)
+            bws_gather_tile(s_base + (is_v ? OFF_V : OFF_K) + st * TILE_B, base, sn, krows, lane);
+            push((is_v ? B_V_FULL : B_K_FULL) + st);
+            HA_T_MARK(2)
 #pragma unroll
-              for (int q = 0; q < 4; ++q) qrows[y][q] = p.q_idx[(long long)seg * p.m_q + (2 * blk + y) * TILE + q * 32 + lane];
+            for (int q = 0; q < 4; ++q) krows[q] = knext[q];
           }
-          if (xg >= 2 && !(ok = wait(B_KV_EMPTY + stage, ((xg >> 1) - 1) & 1))) break;
-          bws_gather_tile(s_base + OFF_KV + stage * 2 * TILE_B, kbase, p.k_sn, krows, lane);
-          bws_gather_tile(s_base + OFF_KV + stage * 2 * TILE_B + TILE_B, vbase, p.v_sn, krows, lane);
-          push(B_KV_FULL + stage);
-          if (x == 0) {
+        }
+        HA_T_DUMP(8, (int)blockIdx.x * 4 + 3, lane == 0 && warp == 12)
+      } else {
+        for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
+          const int seg = item / blocks_per_seg, blk = item - seg * blocks_per_seg;
+          const SegInfo si = seg_info(p, seg);
+          const long long head0 = ((long long)(si.b * p.H + si.h)) * p.n;
+          const uint16_t* qbase = (const uint16_t*)p.q + si.b * p.q_sb + si.h * p.q_sh + si.q_row0 * p.q_sn;
+          const uint16_t* gbase = (const uint16_t*)p.d_o + si.b * p.do_sb + si.h * p.do_sh + si.q_row0 * p.do_sn;
+          const float* lse_base = p.lse + head0 + si.q_row0;
+          const float* delta_base = p.delta + head0 + si.q_row0;
 #pragma unroll
-            for (int y = 0; y < 2; ++y) {
-              if (it >= 1 && !(ok = wait(B_QD_EMPTY + y, (it - 1) & 1))) break;
-              bws_gather_tile(s_base + OFF_QD + y * 2 * TILE_B, qbase, p.q_sn, qrows[y], lane);
-              bws_gather_tile(s_base + OFF_QD + y * 2 * TILE_B + TILE_B, gbase, p.do_sn, qrows[y], lane);
+          for (int y = 0; y < 2; ++y) {
+            int qrows[4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t dst = s_base + OFF_LD + y * 1024 + (q * 32 + lane) * 4;
-                cp_async4(dst, lse_base + qrows[y][q]);
-                cp_async4(dst + 512, delta_base + qrows[y][q]);
-              }
-              push(B_QD_FULL + y);
+            for (int q = 0; q < 4; ++q) qrows[q] = p.q_idx[(long long)seg * p.m_q + (2 * blk + y) * TILE + q * 32 + lane];
+            if (it >= 1 && !(ok = wait(B_QD_EMPTY + y, (it - 1) & 1))) break;
+            bws_gather_tile(s_base + OFF_QD + y * 2 * TILE_B, qbase, p.q_sn, qrows, lane);
+            bws_gather_tile(s_base + OFF_QD + y * 2 * TILE_B + TILE_B, gbase, p.do_sn, qrows, lane);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t dst = s_base + OFF_LD + y * 1024 + (q * 32 + lane) * 4;
+              cp_async4(dst, lse_base + qrows[q]);
+              cp_async4(dst + 512, delta_base + qrows[q]);
+            }
+            push(B_QD_FULL + y);
+          }
+          // The next item's query-side rows: pulled into L2 now, so that the copies issued when their stages come free
+          // (at the very end of this item) find them there instead of in DRAM.
+          const int nitem = item + gridDim.x;
+          if (ok && nitem < n_items) {
+            const int nseg = nitem / blocks_per_seg, nblk = nitem - nseg * blocks_per_seg;
+            const SegInfo ns = seg_info(p, nseg);
+            const uint16_t* nq = (const uint16_t*)p.q + ns.b * p.q_sb + ns.h * p.q_sh + ns.q_row0 * p.q_sn;
+            const uint16_t* ng = (const uint16_t*)p.d_o + ns.b * p.do_sb + ns.h * p.do_sh + ns.q_row0 * p.do_sn;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int qr = p.q_idx[(long long)nseg * p.m_q + 2 * nblk * TILE + j * 32 + lane];
+              prefetch_l2(nq + (int64_t)qr * p.q_sn);
+              prefetch_l2(ng + (int64_t)qr * p.do_sn);
             }
           }
-#pragma unroll
-          for (int q = 0; q < 4; ++q) krows[q] = knext[q];
         }
       }
       cp_async_commit();
       cp_async_wait<0>();      // nothing of this warp is in flight when the CTA retires
     } else if (lane == 0) {
       // ===================================================================================================
-      // MMA issue, three threads.  A single thread gets one tcgen05.mma accepted about every 100 cycles whatever its
-      // shape (measured: 107 cycles per instruction for N <= 128, issue time = completion time), while the tensor pipe
-      // itself finishes an M 128 x N 64 x K 16 step in under 60: so the 40 instructions of a pair are issued from three
-      // threads, each with a product of its own (no accumulator is shared between them):
-      //   warp 13: S^T, dP^T of every half        -> S-ready;   frees (with the others) the K/V and Q/dO stages
-      //   warp 14: dV, dK of every half           -> stage-free, accumulators-full
-      //   warp 15: dQ of every pair               -> dS-buffer-free, dQ-full
-      // Every thread walks the halves / pairs in order and blocks (bounded) on what its next instruction needs.
+      // MMA issue: five threads, one product each (no accumulator is shared between them).  Each walks the halves /
+      // pairs in order and blocks (bounded) on what its next instructions need.
+      //   warp 15: S^T of every half    warp 16: dP^T of every half    -> S-ready (two commits)
+      //   warp 17: dV of every half     warp 18: dK of every half      -> the stage's S^T / dP^T columns free, accumulators full
+      //   warp 19: dQ of every pair                                    -> dS buffer free, dQ full
+      // The "empty" barriers of the operand stages collect one commit from every issuer that reads the stage.
       // ===================================================================================================
       constexpr int AB = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       const int my_items = n_items > (int)blockIdx.x ? (n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
       const uint32_t NH = 4u * (uint32_t)nX;                 // halves per item
       const uint32_t total = (uint32_t)my_items * NH;
-      // Half hh (a count over this CTA's items): item hh / NH, key tile x = (hh % NH) / 4, query tile y = bit 1, column half
-      // g = bit 0.  Pair = hh / 2, key tile count = hh / 4.
+      // Half hh (a count over this CTA's items): item hh / NH, key tile x = (hh % NH) / 4, query tile y = bit 1, stage s = bit 0.
+      // Pair = hh / 2, key tile count = hh / 4.
       bool ok = true;
-      HA_T_DECL(8)
-      if (warp == 13) {
-        const uint32_t id_st = mma_idesc(TILE, 64, AB, 0, 0);      // M = 128 keys, N = 64 queries, both operands K-major
+      if (warp == 15 || warp == 16) {
+        // S^T = K Q^T (warp 15) / dP^T = V dO^T (warp 16) of the half: M = 128 keys, N = 64 query rows, both operands K-major
+        const bool second = warp == 16;
+        const uint32_t id_st = mma_idesc(TILE, 64, AB, 0, 0);
+        HA_T_DECL(8)
         for (uint32_t hh = 0; hh < total && ok; ++hh) {
-          const uint32_t r = hh % NH, itc = hh / NH, x = r >> 2, y = (r >> 1) & 1, g = r & 1;
+          const uint32_t r = hh % NH, itc = hh / NH, x = r >> 2, y = (r >> 1) & 1, s = r & 1;
           const uint32_t pair = hh >> 1, xg = hh >> 2;
           HA_T_MARK(0)
-          if (pair >= 1 && !(ok = wait(B_ST_FREE + g, (pair - 1) & 1))) break;        // dV / dK of the stage's previous half completed
+          // the product that read P^T (dS^T) out of these columns for the stage's previous half has completed
+          if (pair >= 1 && !(ok = wait((second ? B_SF_P : B_SF_S) + s, (pair - 1) & 1))) break;
           HA_T_MARK(1)
-          if ((r & 3) == 0 && !(ok = wait(B_KV_FULL + (xg & 1), (xg >> 1) & 1))) break;
-          if (x == 0 && g == 0 && !(ok = wait(B_QD_FULL + y, itc & 1))) break;
+          const uint32_t ks = xg % K_STAGES, vs = xg & 1;
+          if ((r & 3) == 0 && !(ok = second ? wait(B_V_FULL + vs, (xg >> 1) & 1) : wait(B_K_FULL + ks, (xg / K_STAGES) & 1))) break;
+          if (x == 0 && s == 0 && !(ok = wait(B_QD_FULL + y, itc & 1))) break;
           HA_T_MARK(2)
           fence_async_smem();          // the copies that filled the operand tiles are ordered before the operand reads
           tc_fence_after();
-          const uint32_t sQ = s_base + OFF_QD + y * 2 * TILE_B + g * (TILE_B / 2), sDO = sQ + TILE_B;
-          const uint32_t sK = s_base + OFF_KV + (xg & 1) * 2 * TILE_B, sV = sK + TILE_B;
+          const uint32_t sB = s_base + OFF_QD + y * 2 * TILE_B + s * (TILE_B / 2) + (second ? TILE_B : 0);
+          const uint32_t sA = s_base + (second ? OFF_V + vs * TILE_B : OFF_K + ks * TILE_B);
+          const uint32_t tD = tmem + 128 * s + (second ? 64 : 0);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk)
-            mma_ss(tmem + 128 * g, smem_desc(sK + kk * 32, 16, 1024), smem_desc(sQ + kk * 32, 16, 1024), id_st, kk > 0);
-#pragma unroll
-          for (int kk = 0; kk < DV / 16; ++kk)
-            mma_ss(tmem + 128 * g + 64, smem_desc(sV + kk * 32, 16, 1024), smem_desc(sDO + kk * 32, 16, 1024), id_st, kk > 0);
-          mma_commit(bar(B_S_READY + g));
-          if ((r & 3) == 3) mma_commit(bar(B_KV_EMPTY + (xg & 1)));               // this thread's last read of the K/V stage
-          if (x == (uint32_t)nX - 1 && g == 1) mma_commit(bar(B_QD_EMPTY + y));      // ... and of the Q / dO stage
+          for (int kk = 0; kk < 4; ++kk) mma_ss(tD, smem_desc(sA + kk * 32, 16, 1024), smem_desc(sB + kk * 32, 16, 1024), id_st, kk > 0);
+          mma_commit(bar(B_S_READY + s));
+          if ((r & 3) == 3) mma_commit(bar(second ? B_V_EMPTY + vs : B_K_EMPTY + ks));   // this thread's last read of the K (V) stage
+          if (x == (uint32_t)nX - 1 && s == 1) mma_commit(bar(B_QD_EMPTY + y));      // ... and of the Q / dO stage
           HA_T_MARK(3)
         }
-        HA_T_DUMP(8, (int)blockIdx.x * 4 + 3, true)
-      } else if (warp == 14) {
-        const uint32_t id_kv = mma_idesc(TILE, 64, AB, 0, 1);      // A = P^T / dS^T in TMEM, B = dO / Q rows as MN-major
+        HA_T_DUMP(8, (int)blockIdx.x * 4 + 3, false)
+      } else if (warp == 17 || warp == 18) {
+        // dV += P^T dO (warp 17) / dK += dS^T Q (warp 18) over the half's 64 query rows: A in TMEM, B rows as MN-major
+        const bool second = warp == 18;
+        const uint32_t id_kv = mma_idesc(TILE, 64, AB, 0, 1);
         for (uint32_t hh = 0; hh < total && ok; ++hh) {
-          const uint32_t r = hh % NH, x = r >> 2, y = (r >> 1) & 1, g = r & 1;
+          const uint32_t r = hh % NH, x = r >> 2, y = (r >> 1) & 1, s = r & 1;
           const uint32_t pair = hh >> 1, xg = hh >> 2;
-          if (!(ok = wait(B_P_READY + g, pair & 1))) break;
-          if ((r & 3) == 0 && xg >= 1 && !(ok = wait(B_ACC_FREE, (xg - 1) & 1))) break;    // dV / dK restart with the key tile
+          if (!(ok = wait(B_P_READY + s, pair & 1))) break;
+          if ((r & 3) == 0 && xg >= 1 && !(ok = wait(B_ACC_FREE, (xg - 1) & 1))) break;    // the accumulator restarts with the key tile
           fence_async_smem();
           tc_fence_after();
-          const uint32_t sQ = s_base + OFF_QD + y * 2 * TILE_B + g * (TILE_B / 2), sDO = sQ + TILE_B;
-          const uint32_t tP = tmem + 128 * g, tDS = tP + 64;
+          const uint32_t sB = s_base + OFF_QD + y * 2 * TILE_B + s * (TILE_B / 2) + (second ? 0 : TILE_B);   // Q rows (dK) / dO rows (dV)
+          const uint32_t tA = tmem + 128 * s + (second ? 64 : 0);
+          const uint32_t tD = tmem + (second ? COL_DK : COL_DV);
           const uint32_t acc0 = (r & 3) != 0;
+          // group 0 packed its 32 query columns into TMEM columns [0, 16), group 1 into [32, 48): K steps 0, 1 and 2, 3
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)     // dV += P^T dO over this half's 64 query rows
-            mma_ts(tmem + COL_DV, tP + kk * 8, smem_desc(sDO + kk * 2048, TILE * 128, 1024), id_kv, acc0 | (kk > 0));
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk)     // dK += dS^T Q
-            mma_ts(tmem + COL_DK, tDS + kk * 8, smem_desc(sQ + kk * 2048, TILE * 128, 1024), id_kv, acc0 | (kk > 0));
-          mma_commit(bar(B_ST_FREE + g));
-          if ((r & 3) == 3) mma_commit(bar(B_ACC_FULL));                            // dV / dK of the key tile are complete
-          if (x == (uint32_t)nX - 1 && g == 1) mma_commit(bar(B_QD_EMPTY + y));
+          for (int kk = 0; kk < 4; ++kk)
+            mma_ts(tD, tA + (kk >> 1) * 32 + (kk & 1) * 8, smem_desc(sB + kk * 2048, TILE * 128, 1024), id_kv, acc0 | (kk > 0));
+          mma_commit(bar((second ? B_SF_P : B_SF_S) + s));
+          if ((r & 3) == 3) mma_commit(bar(B_ACC_FULL));                            // the key tile's accumulator is complete
+          if (x == (uint32_t)nX - 1 && s == 1) mma_commit(bar(B_QD_EMPTY + y));
         }
-      } else if (warp == 15) {
-        const uint32_t id_dq = mma_idesc(TILE, 64, AB, 1, 1);      // A = dS ([key][query] rows: MN-major), B = K rows as MN-major
+      } else {
+        // dQ_y += dS K over the pair's 128 keys: A = dS ([key][query] rows: MN-major), B = K rows as MN-major
+        const uint32_t id_dq = mma_idesc(TILE, 64, AB, 1, 1);
         const uint32_t total_pairs = total >> 1;
         for (uint32_t pair = 0; pair < total_pairs && ok; ++pair) {
           const uint32_t r = (2 * pair) % NH, itc = (2 * pair) / NH, x = r >> 2, y = (r >> 1) & 1, xg = pair >> 1;
           // both halves of the pair have written their dS slabs
-          if (!(ok = wait(B_P_READY + 0, pair & 1))) break;
-          if (!(ok = wait(B_P_READY + 1, pair & 1))) break;
+          if (!(ok = wait(B_DS_FULL + (pair & 1), (pair >> 1) & 1))) break;
           if (x == 0 && itc >= 1 && !(ok = wait(B_DQ_FREE + y, (itc - 1) & 1))) break;      // dQ restarts with the item
           fence_async_smem();
           tc_fence_after();
-          const uint32_t sK = s_base + OFF_KV + (xg & 1) * 2 * TILE_B;
+          const uint32_t sK = s_base + OFF_K + (xg % K_STAGES) * TILE_B;
           const uint32_t sDS = s_base + OFF_DS + (pair & 1) * 2 * TILE_B;
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)     // dQ_y += dS K over the 128 keys
+          for (int kk = 0; kk < 8; ++kk)
             mma_ss(tmem + COL_DQ + y * D, smem_desc(sDS + kk * 2048, TILE_B, 1024), smem_desc(sK + kk * 2048, TILE_B, 1024), id_dq,
                    (x > 0) | (kk > 0));
           mma_commit(bar(B_DS_FREE + (pair & 1)));
           if (x == (uint32_t)nX - 1) mma_commit(bar(B_DQ_FULL + y));                  // the query tile's dQ is complete
-          if (y == 1) mma_commit(bar(B_KV_EMPTY + (xg & 1)));                         // this thread's last read of the K tile
+          if (y == 1) mma_commit(bar(B_K_EMPTY + xg % K_STAGES));                     // this thread's last read of the K tile
         }
       }
     }
@@ -481,14 +573,11 @@ int ws_attn_bwd(const ha_attn_params& p, cudaStream_t st) {
   const long long items = segs * blocks_per_seg;
   if (items == 0) return HA_OK;
   if (items * 4 * (2 + p.sample_size / TILE) > 0x7fffffffLL) return HA_ERR_TOO_LARGE;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   const int grid = (int)(items < sms ? items : sms);
 #define HA_BWS_LAUNCH(TT)                                                                                                        \
   do {                                                                                                                           \
-    HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_bwd_ws_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, bws::SMEM),           \
-               "ha_attn_bwd smem attribute");                                                                                    \
+    HA_SMEM_ATTR_ONCE(attn_tc_bwd_ws_kernel<TT>, bws::SMEM, "ha_attn_bwd smem attribute");                                      \
     attn_tc_bwd_ws_kernel<TT><<<grid, bws::THREADS, bws::SMEM, st>>>(p, (int)items, blocks_per_seg);                             \
   } while (0)
   if (p.dtype == HA_BF16) HA_BWS_LAUNCH(__nv_bfloat16);

@@ -502,13 +502,9 @@ static int launch_fwd(const ha_attn_params& p, cudaStream_t st) {
   const int n_qt = (p.m_q + TILE - 1) / TILE;
   if (segs == 0 || n_qt == 0) return HA_OK;
   if (segs > 65535) return HA_ERR_INVALID;
-  // per device, so set on every launch (one process may drive several GPUs)
-  HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_fwd_kernel<T, D, DV, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM),
-             "ha_attn_fwd smem attribute");
+  HA_SMEM_ATTR_ONCE((attn_tc_fwd_kernel<T, D, DV, WT>), Cfg::SMEM, "ha_attn_fwd smem attribute");
   // CTAs resident at once (shared memory and TMEM allow two per SM at head dim 64, one otherwise) = prefetch distance
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   const int pf_dist = p.mode == HA_MODE_HYPER ? sms * (Cfg::TMEM_COLS == 256 ? 2 : 1) : 0;
   attn_tc_fwd_kernel<T, D, DV, WT><<<dim3(n_qt, (unsigned)segs), 128, Cfg::SMEM, st>>>(p, pf_dist);
   HA_LAUNCHED("ha_attn_fwd (tcgen05)");

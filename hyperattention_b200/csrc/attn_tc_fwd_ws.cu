@@ -483,15 +483,12 @@ int ws_attn_fwd(const ha_attn_params& p, cudaStream_t st) {
   const long long items = segs * blocks_per_seg;
   if (items == 0) return HA_OK;
   if (items > 0x7fffffffLL) return HA_ERR_TOO_LARGE;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = sm_count();
   const int grid = (int)(items < sms ? items : sms);
   const bool mg = p.flags & HA_FLAG_MERGE;
 #define HA_WS_LAUNCH(TT, MM)                                                                                                     \
   do {                                                                                                                           \
-    HA_CUDA_OK(cudaFuncSetAttribute(attn_tc_fwd_ws_kernel<TT, MM>, cudaFuncAttributeMaxDynamicSharedMemorySize, ws::SMEM),        \
-               "ha_attn_fwd smem attribute");                                                                                    \
+    HA_SMEM_ATTR_ONCE((attn_tc_fwd_ws_kernel<TT, MM>), ws::SMEM, "ha_attn_fwd smem attribute");                                  \
     attn_tc_fwd_ws_kernel<TT, MM><<<grid, ws::THREADS, ws::SMEM, st>>>(p, (int)items, blocks_per_seg);                           \
   } while (0)
   if (p.dtype == HA_BF16) {

@@ -12,6 +12,9 @@ namespace ha {
 
 constexpr int TILE = 128;           // rows per attention tile (the reference's BLOCK_M = BLOCK_N)
 constexpr int SPIN_LIMIT = 1 << 18;  // poll cap of every device-side wait (a legitimate wait is a few microseconds)
+// ... and its time cap in SM clock cycles (about a second): one try_wait may itself suspend the thread for a
+// hardware-chosen while, so a count of polls alone bounds nothing in practice (measured: minutes)
+constexpr long long WAIT_CYCLES = 2000000000LL;
 
 extern std::atomic<long long> g_launches;
 void set_cuda_error(cudaError_t e, const char* where);
@@ -32,6 +35,34 @@ void set_cuda_error(cudaError_t e, const char* where);
   } while (0)
 
 inline int dtype_size(int dtype) { return dtype == HA_FP32 ? 4 : 2; }
+
+// Number of SMs of the current device, looked up once per device.
+inline int sm_count() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  int v = cache[dev].load(std::memory_order_relaxed);
+  if (v == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    cache[dev].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+// Opt-in dynamic shared memory size of a kernel: a per-device function attribute, set at the first launch on each device
+// (one process may drive several GPUs) instead of before every launch.
+#define HA_SMEM_ATTR_ONCE(kernel, bytes, where)                                                        \
+  do {                                                                                                 \
+    static std::atomic<unsigned long long> _done{0};                                                   \
+    int _dev = 0;                                                                                      \
+    cudaGetDevice(&_dev);                                                                              \
+    const unsigned long long _bit = 1ull << (_dev & 63);                                               \
+    if (!(_done.load(std::memory_order_acquire) & _bit)) {                                             \
+      HA_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes), where); \
+      _done.fetch_or(_bit, std::memory_order_release);                                                 \
+    }                                                                                                  \
+  } while (0)
 
 // ---------------------------------------------------------------------------------------------------
 // element access
@@ -78,8 +109,9 @@ __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("{\n .reg .b64 st;\n mbarrier.arrive.shared::cta.b64 st, [%0];\n}\n" ::"r"(bar) : "memory");
 }
-// Bounded wait: returns false when the phase did not complete within SPIN_LIMIT polls.
+// Bounded wait: returns false when the phase did not complete within SPIN_LIMIT polls or WAIT_CYCLES cycles.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
   for (int i = 0; i < SPIN_LIMIT; ++i) {
     uint32_t ok;
     asm volatile(
@@ -88,6 +120,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     if (ok) return true;
+    if (clock64() - t0 > WAIT_CYCLES) return false;
   }
   return false;
 }
@@ -165,6 +198,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+// 16 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_fence16(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                 "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
