@@ -5,10 +5,10 @@
 // with the same key tiles (the block's two window tiles, then the sampled tiles).  Roles (384 threads):
 //   * group 0 / group 1 (128 threads each): softmax and output of query tile 2b / 2b+1; thread i owns query row i =
 //     TMEM lane i, as in the one-tile kernel (attn_tc_fwd.cu), whose arithmetic this file repeats step for step.
-//   * loader warp: gathers rows by index with 16-byte cp.async into a ring of four K/V stages (each key tile is fetched
-//     once for both query tiles), the two Q tiles (double buffered over the items) and, for a merging call, the rows
-//     already stored for the two query tiles; it runs ahead of the compute
-//     across items, so index -> row latency and the next item's prologue are off the critical path.
+//   * three loader warps (K tiles, V tiles, query side): gather rows by index with 16-byte cp.async into a ring of four
+//     K/V stages (each key tile is fetched once for both query tiles), the two Q tiles (double buffered over the items)
+//     and, for a merging call, the rows already stored for the two query tiles; they run ahead of the compute across
+//     items, so index -> row latency and the next item's prologue are off the critical path.
 //   * MMA warp (one thread): issues S = Q K^T for both groups one key tile ahead of their softmax, and P V as soon as
 //     a group has written P; every completion is a tcgen05.commit onto an mbarrier.
 // TMEM: group g, region r (key tiles alternate): columns 256 g + 128 r; S in 128 fp32 columns, P in place over the
@@ -74,13 +74,13 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
   if (cta_sees_failure(p.status, &s_bail)) return;   // an earlier CTA gave up: drain quickly (uniform over the CTA)
   auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
   if (tid == 0) {
-    // arrivals per phase: 32 (every loader lane, when its copies have landed) on the "full" barriers, 128 (a softmax
-    // group) on P-ready / S-free, 1 (a tcgen05.commit or one elected thread) elsewhere
+    // arrivals per phase: 32 or 64 (every lane of the loaders of that buffer, when its copies have landed) on the "full"
+    // barriers, 128 (a softmax group) on P-ready / S-free, 1 (a tcgen05.commit or one elected thread) elsewhere
     for (int i = 0; i < N_BARS; ++i) {
-      const bool by_loader = (i >= B_KV_FULL && i < B_KV_FULL + KV_STAGES) || (i >= B_Q_FULL && i < B_Q_FULL + 2) ||
-                             (i >= B_OLD_FULL && i < B_OLD_FULL + 2);
+      const bool by_kv_loaders = i >= B_KV_FULL && i < B_KV_FULL + KV_STAGES;    // the K loader's and the V loader's lanes
+      const bool by_loader = (i >= B_Q_FULL && i < B_Q_FULL + 2) || (i >= B_OLD_FULL && i < B_OLD_FULL + 2);
       const bool by_group = (i >= B_P_READY && i < B_PV_READY) || (i >= B_S_FREE && i < B_S_FREE + 4) || i >= B_OLD_EMPTY;
-      mbar_init(bar(i), by_loader ? 32 : by_group ? 128 : 1);
+      mbar_init(bar(i), by_kv_loaders ? 64 : by_loader ? 32 : by_group ? 128 : 1);
     }
     s_abort = 0;
     mbar_fence_init();
@@ -304,63 +304,79 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
     HA_T_DUMP(8, (int)blockIdx.x, tid == 0)
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-    if (warp == 8) {
+    if (warp == 8 || warp == 10) {
       // ===================================================================================================
-      // loader: per item Q tiles, (merge) previous o rows of both tiles, then the key tiles; copy groups complete in
-      // order, a group is signalled once at most LAG younger groups are still in flight
+      // loaders of the key side: K tiles (warp 8) and V tiles (warp 10) of every key tile into the ring.  One warp issuing
+      // every gather of the CTA was its bottleneck (the number of copies a warp has in flight is limited), so the three
+      // operand streams have a warp each.  A stage is full when both warps' copies have landed (64 arrivals).
       // ===================================================================================================
       // The copies of a tile signal its barrier themselves when they land (every lane arrives once, through the copy
-      // engine), so this warp never waits for its own copies: only for free buffers.
+      // engine), so a loader never waits for its own copies: only for free buffers.
       auto push = [&](int b) {
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(b)) : "memory");
       };
+      const bool is_v = warp == 10;
       uint32_t kv_t = 0;      // key tiles fetched so far (ring stage = kv_t % KV_STAGES)
+      bool ok = true;
+      auto load_krows = [&](int seg, int blk, int j, int (&dst)[4]) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int rr = q * 32 + lane;
+          if (j < n_blk) dst[q] = p.k_idx[(long long)seg * p.m_k + (2 * blk + j) * TILE + rr];
+          else {
+            const int s = (j - n_blk) * TILE + rr;
+            dst[q] = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + s] : s;
+          }
+        }
+      };
+      int krows[4] = {-1, -1, -1, -1};
+      if ((int)blockIdx.x < n_items) load_krows(blockIdx.x / blocks_per_seg, blockIdx.x % blocks_per_seg, 0, krows);
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const int seg = item / blocks_per_seg, blk = item - seg * blocks_per_seg;
+        const SegInfo si = seg_info(p, seg);
+        const uint16_t* base = is_v ? (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn
+                                    : (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
+        const int64_t sn = is_v ? p.v_sn : p.k_sn;
+        for (int j = 0; j < n_tiles && ok; ++j, ++kv_t) {
+          const int stage = kv_t % KV_STAGES;
+          // the next tile's row indices (the next item's first tile after this item's last) travel during the wait
+          int knext[4] = {-1, -1, -1, -1};
+          if (j + 1 < n_tiles) load_krows(seg, blk, j + 1, knext);
+          else if (item + (int)gridDim.x < n_items) load_krows((item + gridDim.x) / blocks_per_seg, (item + gridDim.x) % blocks_per_seg, 0, knext);
+          if (kv_t >= KV_STAGES && !(ok = wait(B_KV_EMPTY + stage, ((kv_t / KV_STAGES) - 1) & 1))) break;
+          ws_gather_tile(s_base + OFF_KV + stage * 2 * TILE_B + (is_v ? TILE_B : 0), base, sn, krows, lane);
+          push(B_KV_FULL + stage);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) krows[q] = knext[q];
+        }
+      }
+      cp_async_commit();
+      cp_async_wait<0>();      // nothing of this warp is in flight when the CTA retires
+    } else if (warp == 11) {
+      // ===================================================================================================
+      // loader of the query side: per item the two Q tiles and, for a merging call, the rows already stored for them
+      // ===================================================================================================
+      auto push = [&](int b) {
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar(b)) : "memory");
+      };
       bool ok = true;
       int it = 0;
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
         const int seg = item / blocks_per_seg, blk = item - seg * blocks_per_seg;
         const SegInfo si = seg_info(p, seg);
         const uint16_t* qbase = (const uint16_t*)p.q + si.b * p.q_sb + si.h * p.q_sh + si.q_row0 * p.q_sn;
-        const uint16_t* kbase = (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
-        const uint16_t* vbase = (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn;
         int qrows[2][4];
 #pragma unroll
         for (int x = 0; x < 2; ++x)
 #pragma unroll
           for (int q = 0; q < 4; ++q) qrows[x][q] = p.q_idx[(long long)seg * p.m_q + (2 * blk + x) * TILE + q * 32 + lane];
-        // index rows of the first key tile, loaded ahead of the Q gathers
-        int krows[4];
-        auto load_krows = [&](int j, int (&dst)[4]) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int rr = q * 32 + lane;
-            if (j < n_blk) dst[q] = p.k_idx[(long long)seg * p.m_k + (2 * blk + j) * TILE + rr];
-            else {
-              const int s = (j - n_blk) * TILE + rr;
-              dst[q] = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + s] : s;
-            }
-          }
-        };
-        load_krows(0, krows);
         const int qb = it & 1;                                                // Q buffer of this item
         if (it >= 2 && !(ok = wait(B_Q_EMPTY + qb, ((it >> 1) - 1) & 1))) break;   // its previous user's S MMAs are through
         ws_gather_tile(s_base + OFF_Q + qb * 2 * TILE_B, qbase, p.q_sn, qrows[0], lane);
         ws_gather_tile(s_base + OFF_Q + qb * 2 * TILE_B + TILE_B, qbase, p.q_sn, qrows[1], lane);
         push(B_Q_FULL + qb);
-        for (int j = 0; j < n_tiles && ok; ++j, ++kv_t) {
-          const int stage = kv_t % KV_STAGES;
-          int knext[4] = {-1, -1, -1, -1};
-          if (j + 1 < n_tiles) load_krows(j + 1, knext);
-          if (kv_t >= KV_STAGES && !(ok = wait(B_KV_EMPTY + stage, ((kv_t / KV_STAGES) - 1) & 1))) break;
-          ws_gather_tile(s_base + OFF_KV + stage * 2 * TILE_B, kbase, p.k_sn, krows, lane);
-          ws_gather_tile(s_base + OFF_KV + stage * 2 * TILE_B + TILE_B, vbase, p.v_sn, krows, lane);
-          push(B_KV_FULL + stage);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) krows[q] = knext[q];
-        }
-        // (merge) the rows stored before this call, needed in the item's epilogue only: fetched last, so that waiting
-        // for the previous item's epilogue to release the buffer does not hold up this item's key tiles
-        if (merge && ok) {
+        // (merge) the rows stored before this call, needed in the item's epilogue only
+        if (merge) {
           const uint16_t* obase = (const uint16_t*)p.o + si.b * p.o_sb + si.h * p.o_sh + si.q_row0 * p.o_sn;
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
@@ -371,7 +387,7 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
         }
       }
       cp_async_commit();
-      cp_async_wait<0>();      // nothing of this warp is in flight when the CTA retires
+      cp_async_wait<0>();
     } else if (warp == 9 && lane == 0) {
       // ===================================================================================================
       // MMA issue
