@@ -72,6 +72,10 @@ SIGNATURES = {
     'ha_delta': (C.c_int, [vp, i64, i64, i64, vp, i64, i64, i64, i32, i32, i32, i32, i32, vp, vp]),
     'ha_cast_from_f32': (C.c_int, [vp, vp, i64, i32, vp]),
     'ha_lse_merge': (C.c_int, [vp, vp, vp, vp, i64, i32, i32, i32, vp]),
+    'ha_noncausal_saved_bytes': (i64, [C.POINTER(CausalParams)]),
+    'ha_noncausal_scratch_bytes': (i64, [C.POINTER(CausalParams), i32]),
+    'ha_noncausal_fwd': (C.c_int, [C.POINTER(CausalParams), vp]),
+    'ha_noncausal_bwd': (C.c_int, [C.POINTER(CausalParams), vp]),
     'ha_wait_probe': (C.c_int, [vp, vp, i32, vp]),
     'ha_causal_saved_bytes': (i64, [C.POINTER(CausalParams)]),
     'ha_causal_scratch_bytes': (i64, [C.POINTER(CausalParams), i32]),

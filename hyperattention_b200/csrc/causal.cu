@@ -86,7 +86,8 @@ __global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ 
   const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int dv = lpr * EPC;
-  constexpr int UN = 4;   // row groups per iteration: keeps several independent loads in flight per lane
+  constexpr int UN = 2;   // row groups per iteration
+  constexpr int PG = 4;   // parts whose rows are requested together: UN * (PG + 1) independent 16-byte loads in flight per lane
   for (long long base = warp_id * rpw * UN; base < total_rows; base += n_warps * rpw * UN) {
     long long row[UN];
     bool ok[UN];
@@ -100,31 +101,40 @@ __global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ 
       g[u] = make_uint4(0, 0, 0, 0);
       if (ok[u]) g[u] = __ldg(reinterpret_cast<const uint4*>(d_o + row[u] * dv + chunk * EPC));
     }
-    for (int part = 0; part <= levels; ++part) {
-      bool need[UN];
-      uint4 a[UN];
+    for (int part0 = 0; part0 <= levels; part0 += PG) {
+      bool need[PG][UN];
+      uint4 a[PG][UN];
 #pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        need[u] = ok[u] && (part == levels || ((i[u] / (n >> (part + 1))) & 1));
-        a[u] = make_uint4(0, 0, 0, 0);
-        if (need[u]) a[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(parts0 + part * part_stride_bytes) + row[u] * dv + chunk * EPC));
+      for (int pp = 0; pp < PG; ++pp) {
+        const int part = part0 + pp;
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+          need[pp][u] = part <= levels && ok[u] && (part == levels || ((i[u] / (n >> (part + 1))) & 1));
+          a[pp][u] = make_uint4(0, 0, 0, 0);
+          if (need[pp][u])
+            a[pp][u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(parts0 + part * part_stride_bytes) + row[u] * dv + chunk * EPC));
+        }
       }
 #pragma unroll
-      for (int u = 0; u < UN; ++u) {
-        float s = 0.f;
-        const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, gw[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+      for (int pp = 0; pp < PG; ++pp) {
+        const int part = part0 + pp;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          if constexpr (EPC == 8) {
-            const float2 fa = unpack2<T>(aw[w]), fg = unpack2<T>(gw[w]);
-            s = fmaf(fa.x, fg.x, s);
-            s = fmaf(fa.y, fg.y, s);
-          } else {
-            s = fmaf(__uint_as_float(aw[w]), __uint_as_float(gw[w]), s);
+        for (int u = 0; u < UN; ++u) {
+          float s = 0.f;
+          const uint32_t aw[4] = {a[pp][u].x, a[pp][u].y, a[pp][u].z, a[pp][u].w}, gw[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            if constexpr (EPC == 8) {
+              const float2 fa = unpack2<T>(aw[w]), fg = unpack2<T>(gw[w]);
+              s = fmaf(fa.x, fg.x, s);
+              s = fmaf(fa.y, fg.y, s);
+            } else {
+              s = fmaf(__uint_as_float(aw[w]), __uint_as_float(gw[w]), s);
+            }
           }
+          for (int off = lpr >> 1; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+          if (need[pp][u] && chunk == 0) delta[(long long)part * total_rows + row[u]] = s;
         }
-        for (int off = lpr >> 1; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-        if (need[u] && chunk == 0) delta[(long long)part * total_rows + row[u]] = s;
       }
     }
   }
@@ -305,7 +315,7 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
     const int es = dtype_size(p.dtype), epc = 16 / es, lpr = p.dv / epc;
     if (p.dv % epc == 0 && (lpr == 2 || lpr == 4 || lpr == 8 || lpr == 16 || lpr == 32) && (uintptr_t)p.d_o % 16 == 0) {
       const long long part_stride = (uint8_t*)sv.part_o(1) - (uint8_t*)sv.part_o(0);
-      const long long per_cta = 8LL * (32 / lpr) * 4;
+      const long long per_cta = 8LL * (32 / lpr) * 2;
       long long want = (pl.rows + per_cta - 1) / per_cta;
       const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
       if (p.dtype == HA_BF16)
@@ -351,6 +361,157 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
   rc = ha_cast_from_f32(dk_acc, p.dk, pl.rows * p.d, p.dtype, stream);
   if (rc != HA_OK) return rc;
   return ha_cast_from_f32(dv_acc, p.dv_out, pl.rows * p.dv, p.dtype, stream);
+}
+
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * The non-causal module call (forward_no_causal_mask, hyper_attention.py:103-132, on sequences of at least min_seq_len)
+ * as one call: hash q and k, sort both (one segmented sort over 2 B H rows), attention; and its backward: delta, the
+ * backward kernel with whatever direct outputs it supports, the finishing pass.  Same parameter struct as the causal
+ * schedule (levels, keep_parts, min_seq_len unused).
+ * saved: q_idx | k_idx.  scratch: forward = codes of q and k + sort workspace; backward = delta + slot buffers / fp32
+ * accumulators as the backward kernel needs them.
+ * --------------------------------------------------------------------------------------------------------------- */
+static int noncausal_check(const ha_causal_params& p, long long& rows) {
+  if (p.dtype != HA_BF16 && p.dtype != HA_FP16 && p.dtype != HA_FP32) return HA_ERR_DTYPE;
+  if (p.B <= 0 || p.H <= 0 || p.n <= 0 || p.d <= 0 || p.dv <= 0 || p.d > 256 || p.dv > 256) return HA_ERR_INVALID;
+  if (p.lsh_bits < 1 || p.lsh_bits > 16 || p.n % TILE != 0) return HA_ERR_INVALID;
+  if (p.sample_size < 0 || p.sample_size % TILE != 0 || p.sample_size > p.n || p.block_size < 1) return HA_ERR_INVALID;
+  rows = (long long)p.B * p.H * p.n;
+  return HA_OK;
+}
+
+static void noncausal_attn(const ha_causal_params& p, ha_attn_params& a, long long rows) {
+  fill_attn(p, a);
+  a.mode = HA_MODE_HYPER;
+  a.flags = p.flags & (HA_FLAG_SMOOTH | HA_FLAG_BWD_REF_SMOOTH | HA_FLAG_FORCE_SIMT | HA_FLAG_NO_WS);
+  a.segs_per_head = 1;
+  a.span = p.n; a.q_off = 0; a.k_off = 0; a.m_q = p.n; a.m_k = p.n;
+  a.q_idx = (const int32_t*)p.saved;
+  a.k_idx = (const int32_t*)((const uint8_t*)p.saved + align256(rows * 4));
+}
+
+// what the backward needs beyond delta: 2 = slot buffers only, 1 = slot buffers + fp32 dQ, 0 = three fp32 accumulators
+static int noncausal_bwd_level(const ha_causal_params& p, long long rows) {
+  ha_attn_params a;
+  noncausal_attn(p, a, rows);
+  float dummy = 0.f;
+  a.delta = &dummy;                               // (only looked at for being there)
+  a.dq_acc = a.dk_acc = a.dv_acc = nullptr;
+  return p.dtype == HA_FP32 ? 0 : ha_attn_bwd_direct_level(&a);
+}
+
+int64_t ha_noncausal_saved_bytes(const ha_causal_params* p) {
+  long long rows;
+  if (!p || noncausal_check(*p, rows) != HA_OK) return -1;
+  return 2 * align256(rows * 4);
+}
+
+int64_t ha_noncausal_scratch_bytes(const ha_causal_params* p, int32_t backward) {
+  long long rows;
+  if (!p || noncausal_check(*p, rows) != HA_OK) return -1;
+  if (!backward) return 2 * align256(rows * 4) + align256(ha_seg_sort_workspace_bytes(2 * p->B * p->H, p->n, p->n, p->n, p->lsh_bits));
+  const int level = noncausal_bwd_level(*p, rows);
+  const long long sacc = align256((long long)p->B * p->H * p->sample_size * (p->d + p->dv) * 4);
+  long long bytes = align256(rows * 4);
+  if (level == 2) bytes += sacc;
+  else if (level == 1) bytes += sacc + align256(rows * p->d * 4);
+  else bytes += 2 * align256(rows * p->d * 4) + align256(rows * p->dv * 4);
+  return bytes;
+}
+
+int ha_noncausal_fwd(const ha_causal_params* pp, void* stream) {
+  if (!pp) return HA_ERR_INVALID;
+  const ha_causal_params& p = *pp;
+  long long rows;
+  int rc = noncausal_check(p, rows);
+  if (rc != HA_OK) return rc;
+  if (!p.q || !p.k || !p.v || !p.o || !p.lse || !p.proj) return HA_ERR_INVALID;
+  if (!p.saved || p.saved_bytes < ha_noncausal_saved_bytes(pp)) return HA_ERR_WORKSPACE;
+  if (!p.scratch || p.scratch_bytes < ha_noncausal_scratch_bytes(pp, 0)) return HA_ERR_WORKSPACE;
+  // codes of q and k side by side: one segmented sort call covers both, and its output is q_idx | k_idx -- if the two
+  // halves of `saved` are contiguous, which they are when rows * 4 is a multiple of 256 (n is a multiple of 128)
+  int32_t* codes = (int32_t*)p.scratch;
+  void* sort_ws = (uint8_t*)p.scratch + 2 * align256(rows * 4);
+  const long long sort_ws_bytes = p.scratch_bytes - 2 * align256(rows * 4);
+  const int64_t sn = p.d, sh = (int64_t)p.n * p.d, sb = sh * p.H;
+  rc = ha_lsh_hash(p.q, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes, stream);
+  if (rc != HA_OK) return rc;
+  rc = ha_lsh_hash(p.k, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes + rows, stream);
+  if (rc != HA_OK) return rc;
+  if (align256(rows * 4) == rows * 4) {
+    rc = ha_seg_sort(codes, 2 * p.B * p.H, p.n, p.n, 0, p.n, p.lsh_bits, (int32_t*)p.saved, sort_ws, sort_ws_bytes, stream);
+  } else {
+    rc = ha_seg_sort(codes, p.B * p.H, p.n, p.n, 0, p.n, p.lsh_bits, (int32_t*)p.saved, sort_ws, sort_ws_bytes, stream);
+    if (rc == HA_OK)
+      rc = ha_seg_sort(codes + rows, p.B * p.H, p.n, p.n, 0, p.n, p.lsh_bits, (int32_t*)((uint8_t*)p.saved + align256(rows * 4)), sort_ws,
+                       sort_ws_bytes, stream);
+  }
+  if (rc != HA_OK) return rc;
+  ha_attn_params a;
+  noncausal_attn(p, a, rows);
+  return ha_attn_fwd(&a, stream);
+}
+
+int ha_noncausal_bwd(const ha_causal_params* pp, void* stream) {
+  if (!pp) return HA_ERR_INVALID;
+  const ha_causal_params& p = *pp;
+  long long rows;
+  int rc = noncausal_check(p, rows);
+  if (rc != HA_OK) return rc;
+  if (!p.q || !p.k || !p.v || !p.o || !p.lse || !p.d_o || !p.dq || !p.dk || !p.dv_out) return HA_ERR_INVALID;
+  if (!p.saved || p.saved_bytes < ha_noncausal_saved_bytes(pp)) return HA_ERR_WORKSPACE;
+  if (!p.scratch || p.scratch_bytes < ha_noncausal_scratch_bytes(pp, 1)) return HA_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  uint8_t* s = (uint8_t*)p.scratch;
+  float* delta = (float*)s;                  s += align256(rows * 4);
+  ha_attn_params a;
+  noncausal_attn(p, a, rows);
+  a.delta = delta;
+  rc = ha_delta(p.o, a.o_sb, a.o_sh, a.o_sn, p.d_o, a.do_sb, a.do_sh, a.do_sn, p.B, p.H, p.n, p.dv, p.dtype, delta, stream);
+  if (rc != HA_OK) return rc;
+  const int level = noncausal_bwd_level(p, rows);
+  if (level >= 1) {
+    const long long segs = (long long)p.B * p.H;
+    const long long sacc_bytes = segs * p.sample_size * (p.d + p.dv) * 4;
+    a.dk_sacc = (float*)s;
+    a.dv_sacc = a.dk_sacc + segs * p.sample_size * p.d;
+    s += align256(sacc_bytes);
+    if (sacc_bytes > 0) HA_CUDA_OK(cudaMemsetAsync(a.dk_sacc, 0, sacc_bytes, st), "ha_noncausal_bwd memset");
+    a.dk_out = p.dk;
+    a.dv_out = p.dv_out;
+    if (level == 2) {
+      a.dq_out = p.dq;
+    } else {
+      a.dq_acc = (float*)s;
+      HA_CUDA_OK(cudaMemsetAsync(a.dq_acc, 0, rows * p.d * 4, st), "ha_noncausal_bwd memset");
+    }
+    rc = ha_attn_bwd(&a, stream);
+    if (rc != HA_OK) return rc;
+    rc = ha_attn_bwd_finish(&a, stream);
+    if (rc != HA_OK) return rc;
+    if (level == 1) rc = ha_cast_from_f32(a.dq_acc, p.dq, rows * p.d, p.dtype, stream);
+    return rc;
+  }
+  a.dq_acc = (float*)s;                      s += align256(rows * p.d * 4);
+  a.dk_acc = (float*)s;                      s += align256(rows * p.d * 4);
+  a.dv_acc = (float*)s;
+  HA_CUDA_OK(cudaMemsetAsync(a.dq_acc, 0, rows * p.d * 4, st), "ha_noncausal_bwd memset");
+  HA_CUDA_OK(cudaMemsetAsync(a.dk_acc, 0, rows * p.d * 4, st), "ha_noncausal_bwd memset");
+  HA_CUDA_OK(cudaMemsetAsync(a.dv_acc, 0, rows * p.dv * 4, st), "ha_noncausal_bwd memset");
+  rc = ha_attn_bwd(&a, stream);
+  if (rc != HA_OK) return rc;
+  if (p.dtype == HA_FP32) {
+    HA_CUDA_OK(cudaMemcpyAsync(p.dq, a.dq_acc, rows * p.d * 4, cudaMemcpyDeviceToDevice, st), "ha_noncausal_bwd copy");
+    HA_CUDA_OK(cudaMemcpyAsync(p.dk, a.dk_acc, rows * p.d * 4, cudaMemcpyDeviceToDevice, st), "ha_noncausal_bwd copy");
+    HA_CUDA_OK(cudaMemcpyAsync(p.dv_out, a.dv_acc, rows * p.dv * 4, cudaMemcpyDeviceToDevice, st), "ha_noncausal_bwd copy");
+    return HA_OK;
+  }
+  rc = ha_cast_from_f32(a.dq_acc, p.dq, rows * p.d, p.dtype, stream);
+  if (rc != HA_OK) return rc;
+  rc = ha_cast_from_f32(a.dk_acc, p.dk, rows * p.d, p.dtype, stream);
+  if (rc != HA_OK) return rc;
+  return ha_cast_from_f32(a.dv_acc, p.dv_out, rows * p.dv, p.dtype, stream);
 }
 
 }  // extern "C"

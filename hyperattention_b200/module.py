@@ -9,6 +9,9 @@ Additional keyword arguments (all optional, accepted through **kwargs like the r
   rng         torch.Generator used to draw proj_dir (the reference's AngularLSHTriton has the same argument).
   fused_causal  True (default): run regular causal shapes through the single-call schedule; False: always use the
               per-level path built from the individual operators.
+  fused_calls True (default): a non-causal call on contiguous inputs is one library call each way (hash, sort and attention;
+              delta, backward and finishing pass); False: one call per operator, as strided inputs and the uniform
+              sampling mode always do.
 """
 import math
 
@@ -76,6 +79,7 @@ class HyperAttention(torch.nn.Module):
         self.grad_mode = kwargs.get('grad_mode', 'reference')
         self.merge_mode = kwargs.get('merge_mode', 'reference')
         self.fused_causal = kwargs.get('fused_causal', True)
+        self.fused_calls = kwargs.get('fused_calls', True)
         self.kernel_flags = kwargs.get('kernel_flags', 0)
         # 'reference': sampled part = key rows 0..sample_size-1, unweighted (what the reference's kernels compute).
         # 'uniform':   sample_size distinct key rows per (batch, head), one uniform draw per stratum, the query tile's own block
@@ -177,6 +181,12 @@ class HyperAttention(torch.nn.Module):
         if self.min_seq_len > n_query:
             attn, lse = ops.flash_attn_func(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2), None, False,
                                             scale, self.kernel_flags & L.FLAG_FORCE_SIMT)
+        elif self.sampling == 'reference' and self.fused_calls and query.is_contiguous() and key.is_contiguous() \
+                and value.is_contiguous() and query.dtype == self.lsh.proj_dir.dtype:
+            # hash, sort, attention (and, in the backward, delta, the backward kernel, the finishing pass) in one library call
+            attn, lse = ops.NonCausalHyperFunc.apply(query, key, value, self.lsh.proj_f32(), self.block_size, self.sample_size,
+                                                     scale, self._flags())
+            return attn, lse.unsqueeze(-1)
         else:
             bits = self.lsh_num_projs
             # codes of q and k side by side: one segmented sort call covers both

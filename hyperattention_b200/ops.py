@@ -518,5 +518,76 @@ class CausalHyperFunc(torch.autograd.Function):
         return dq, dk, dvv, None, None, None, None, None, None, None, None
 
 
+class NonCausalHyperFunc(torch.autograd.Function):
+    """forward_no_causal_mask on sequences of at least min_seq_len (hyper_attention.py:116-130: hash, stable sort,
+    hyper_attn_func) as ONE library call each way (ha_noncausal_fwd / ha_noncausal_bwd) on contiguous [B, H, n, *] tensors:
+    two calls into the library per training step instead of nine, which is what bounds the step when a rank owns few
+    heads.  Returns o [B, H, n, dv] and lse [B, H, n]; the gradient flowing into lse is discarded, as in the reference."""
+
+    @staticmethod
+    def _params(q, k, v, proj_f32, block_size, sample_size, scale, flags):
+        B, H, n, d = q.shape
+        p = L.CausalParams()
+        p.dtype, p.flags = _dtype_id(q), flags
+        p.B, p.H, p.n, p.d, p.dv = B, H, n, d, v.shape[-1]
+        p.block_size, p.sample_size, p.lsh_bits, p.scale = block_size, sample_size, proj_f32.shape[1], scale
+        p.q, p.k, p.v, p.proj = _ptr(q), _ptr(k), _ptr(v), _ptr(proj_f32)
+        _set_status(p, q.device)
+        return p
+
+    @staticmethod
+    def forward(ctx, q, k, v, proj_f32, block_size, sample_size, scale, flags):
+        _cuda(q, k, v, proj_f32)
+        assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+        assert q.dtype == k.dtype == v.dtype, 'All tensors must have the same type'
+        B, H, n, d = q.shape
+        assert k.shape == (B, H, n, d), 'query and key sequence lengths must be equal'
+        assert n % 128 == 0, 'keys sequence length must be divisible by 128'
+        assert sample_size % 128 == 0
+        dev = q.device
+        o = torch.empty(B, H, n, v.shape[-1], dtype=q.dtype, device=dev)
+        lse = torch.empty(B, H, n, dtype=torch.float32, device=dev)
+        p = NonCausalHyperFunc._params(q, k, v, proj_f32, block_size, sample_size, scale, flags)
+        p.o, p.lse = _ptr(o), _ptr(lse)
+        lib = L.load()
+        saved_bytes, scratch_bytes = lib.ha_noncausal_saved_bytes(C.byref(p)), lib.ha_noncausal_scratch_bytes(C.byref(p), 0)
+        assert saved_bytes >= 0 and scratch_bytes >= 0, 'shape not accepted (n and sample_size multiples of 128, sample_size <= n)'
+        saved = torch.empty(saved_bytes, dtype=torch.uint8, device=dev)
+        scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=dev)
+        p.saved, p.saved_bytes, p.scratch, p.scratch_bytes = _ptr(saved), saved_bytes, _ptr(scratch), scratch_bytes
+        with torch.cuda.device(dev):
+            rc = lib.ha_noncausal_fwd(C.byref(p), _stream())
+        L.check(rc, 'ha_noncausal_fwd')
+        ctx.save_for_backward(q, k, v, o, lse, saved, proj_f32)
+        ctx.cfg = (block_size, sample_size, scale, flags)
+        ctx.set_materialize_grads(False)
+        return o, lse
+
+    @staticmethod
+    def backward(ctx, do, dlse_unused=None):
+        q, k, v, o, lse, saved, proj_f32 = ctx.saved_tensors
+        block_size, sample_size, scale, flags = ctx.cfg
+        if do is None:
+            return (None,) * 8
+        do = do.contiguous()
+        dev = q.device
+        # one buffer for the three gradients (dq | dk | dv): one allocation per step
+        nq, nv = q.numel(), v.numel()
+        out = torch.empty(2 * nq + nv, dtype=q.dtype, device=dev)
+        dq, dk, dvv = out[:nq].view_as(q), out[nq:2 * nq].view_as(k), out[2 * nq:].view_as(v)
+        p = NonCausalHyperFunc._params(q, k, v, proj_f32, block_size, sample_size, scale, flags)
+        p.o, p.lse = _ptr(o), _ptr(lse)
+        p.saved, p.saved_bytes = _ptr(saved), saved.numel()
+        p.d_o, p.dq, p.dk, p.dv_out = _ptr(do), _ptr(dq), _ptr(dk), _ptr(dvv)
+        lib = L.load()
+        scratch_bytes = lib.ha_noncausal_scratch_bytes(C.byref(p), 1)
+        scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=dev)
+        p.scratch, p.scratch_bytes = _ptr(scratch), scratch_bytes
+        with torch.cuda.device(dev):
+            rc = lib.ha_noncausal_bwd(C.byref(p), _stream())
+        L.check(rc, 'ha_noncausal_bwd')
+        return dq, dk, dvv, None, None, None, None, None
+
+
 def launch_count():
     return int(L.load().ha_launch_count())

@@ -233,6 +233,16 @@ int64_t ha_causal_scratch_bytes(const ha_causal_params* p, int32_t backward);
 int ha_causal_fwd(const ha_causal_params* p, void* stream);
 int ha_causal_bwd(const ha_causal_params* p, void* stream);
 
+/* The non-causal module call in one call each way.  Replaces forward_no_causal_mask on sequences of at least
+ * min_seq_len (hyper_attention.py:103-132: hash, stable sort, hyper_attn_func) and its backward (delta, the backward kernel
+ * with the direct outputs it supports, the finishing pass), on contiguous [B,H,n,*] tensors, sampled rows 0..sample_size-1.
+ * Takes the same parameter struct as the causal schedule; levels, keep_parts and min_seq_len are not looked at.  saved holds the two sort permutations
+ * (needed again by the backward); scratch is free after each call. */
+int64_t ha_noncausal_saved_bytes(const ha_causal_params* p);
+int64_t ha_noncausal_scratch_bytes(const ha_causal_params* p, int32_t backward);
+int ha_noncausal_fwd(const ha_causal_params* p, void* stream);
+int ha_noncausal_bwd(const ha_causal_params* p, void* stream);
+
 /* Diagnostic for the timeout path.  One warp polls an mbarrier that nothing ever arrives at, `polls` times (1..2^18),
  * gives up and reports HA_DEV_TIMEOUT through status / status_host exactly as the attention kernels do when one of their
  * bounded waits runs out.  No copy and no tensor-core operation is in flight; the kernel returns normally and the

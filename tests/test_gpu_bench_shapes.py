@@ -199,3 +199,26 @@ def test_device_timeout_reaches_the_host_as_an_exception():
     assert torch.isfinite(o).all()
     ha.check_device_status()
     assert ha.lsh_hash(x, proj).shape == (1, 1, 256)
+
+
+@pytest.mark.parametrize('dtype,smooth', [(torch.bfloat16, False), (torch.float16, True), (torch.float32, False)])
+def test_single_call_noncausal_path_matches_per_operator_path(dtype, smooth):
+    """ha_noncausal_fwd / ha_noncausal_bwd (hash, sort, attention; delta, backward, finishing pass in one library call
+    each way) against the same module calling one operator at a time: identical forward, gradients equal up to the order
+    of fp32 additions; and far fewer calls into the library."""
+    import hyperattention_b200 as ha
+    torch.manual_seed(64)
+    B, H, n, d = 2, 3, 2048, 64
+    q, k, v, do = [torch.randn(B, H, n, d, device='cuda').to(dtype) for _ in range(4)]
+    outs = []
+    for fused in (True, False):
+        mod = ha.HyperAttention(input_dim=d, block_size=256, sample_size=256, min_seq_len=512, smooth_block=smooth, fused_calls=fused,
+                                rng=torch.Generator().manual_seed(6)).to(device='cuda', dtype=dtype)
+        qg, kg, vg = [t.clone().requires_grad_() for t in (q, k, v)]
+        o, lse = mod(qg, kg, vg, return_lse=True)
+        assert o.shape == (B, H, n, d) and lse.shape == (B, H, n, 1)
+        o.backward(do)
+        outs.append((o.detach(), lse.detach(), qg.grad, kg.grad, vg.grad))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    for a, b in zip(outs[0][2:], outs[1][2:]):
+        assert rel(a, b) < 1e-3
