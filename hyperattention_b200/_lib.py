@@ -27,7 +27,7 @@ class AttnParams(C.Structure):
         ('mode', i32), ('flags', i32), ('dtype', i32),
         ('B', i32), ('H', i32), ('n', i32), ('d', i32), ('dv', i32),
         ('segs_per_head', i32), ('span', i32), ('q_off', i32), ('k_off', i32), ('m_q', i32), ('m_k', i32),
-        ('block_size', i32), ('sample_size', i32), ('scale', f32),
+        ('block_size', i32), ('sample_size', i32), ('kv_group', i32), ('scale', f32),
         ('q', vp), ('k', vp), ('v', vp),
         ('q_sb', i64), ('q_sh', i64), ('q_sn', i64), ('k_sb', i64), ('k_sh', i64), ('k_sn', i64),
         ('v_sb', i64), ('v_sh', i64), ('v_sn', i64),
@@ -47,7 +47,7 @@ class CausalParams(C.Structure):
         ('dtype', i32), ('flags', i32),
         ('B', i32), ('H', i32), ('n', i32), ('d', i32), ('dv', i32),
         ('levels', i32), ('block_size', i32), ('sample_size', i32), ('lsh_bits', i32), ('keep_parts', i32),
-        ('min_seq_len', i32), ('scale', f32),
+        ('min_seq_len', i32), ('kv_group', i32), ('scale', f32),
         ('q', vp), ('k', vp), ('v', vp), ('proj', vp), ('o', vp), ('lse', vp),
         ('saved', vp), ('saved_bytes', i64), ('scratch', vp), ('scratch_bytes', i64),
         ('d_o', vp), ('dq', vp), ('dk', vp), ('dv_out', vp), ('status', vp), ('status_host', vp),

@@ -23,6 +23,12 @@ static int check_common(const ha_attn_params& p, bool backward) {
   // a single-segment exact-attention call may have more keys than queries (n describes the query side then)
   if (p.k_off + p.m_k > p.span && !(p.mode == HA_MODE_FLASH && p.segs_per_head == 1 && !backward)) return HA_ERR_INVALID;
   if (!p.q || !p.k || !p.v || !p.o || !p.lse) return HA_ERR_INVALID;
+  if (p.kv_group < 0 || (p.kv_group > 1 && p.H % p.kv_group != 0)) return HA_ERR_INVALID;
+  if (p.kv_group > 1) {
+    // a K/V row collects gradient terms from every query head of its group: fp32 accumulators only, nothing "stored once";
+    // the per-tile sample weights are computed per query head and not offered together with shared K/V heads
+    if (p.dk_out || p.dv_out || p.dq_out || (p.flags & HA_FLAG_BWD_KV_INIT) || p.sample_logw) return HA_ERR_INVALID;
+  }
   if (p.mode == HA_MODE_HYPER) {
     // the reference asserts: equal lengths, multiples of 128 (src/hyper_attn_triton.py:695, :911)
     if (p.m_q != p.m_k || p.m_q % TILE != 0) return HA_ERR_INVALID;
@@ -62,12 +68,12 @@ __global__ void bwd_finish_kernel(const ha_attn_params p, long long total) {
   const long long ss = i / cpr;
   const int slot = (int)(ss % p.sample_size), seg = (int)(ss / p.sample_size);
   const SegInfo si = seg_info(p, seg);
-  const int row = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + slot] : slot;
+  const int row = p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + slot] : slot;
   const long long out_row = ((long long)(si.b * p.H + si.h)) * p.n + si.k_row0 + row;
   const bool is_k = c < cpr_k;
   const int w = is_k ? p.d : p.dv, e0 = (is_k ? c : c - cpr_k) * 8;
   T* out = (is_k ? (T*)p.dk_out : (T*)p.dv_out) + out_row * w + e0;
-  const float* acc = (is_k ? p.dk_sacc : p.dv_sacc) + ((long long)seg * p.sample_size + slot) * w + e0;
+  const float* acc = (is_k ? p.dk_sacc : p.dv_sacc) + (kseg_of(p, seg) * p.sample_size + slot) * w + e0;
   uint4 raw = *reinterpret_cast<const uint4*>(out);
   T* v = reinterpret_cast<T*>(&raw);
   const float4 a0 = *reinterpret_cast<const float4*>(acc), a1 = *reinterpret_cast<const float4*>(acc + 4);
@@ -127,7 +133,7 @@ int ha_attn_bwd(const ha_attn_params* p, void* stream) {
 }
 
 int ha_attn_bwd_direct_level(const ha_attn_params* p) {
-  if (!p || !p->d_o || p->mode != HA_MODE_HYPER) return 0;
+  if (!p || !p->d_o || p->mode != HA_MODE_HYPER || p->kv_group > 1) return 0;
   if ((p->flags & HA_FLAG_FORCE_SIMT) || !tc_bwd_supported(*p)) return 0;
   if (ws_bwd_shape_ok(*p)) return 2;   // the warp-specialised kernel sums every query tile's dQ inside one work item
   const bool whole_blocks = !(p->flags & HA_FLAG_SMOOTH) && (p->block_size + TILE - 1) / TILE == 2 && p->m_k % (2 * TILE) == 0;

@@ -7,7 +7,9 @@ namespace ha {
 
 struct SegInfo {
   long long q_row0, k_row0;   // first query / key row of the segment inside its head (in rows)
+  long long khead0;           // first row of the segment's K/V head in a contiguous [B, H_kv, n, *] tensor (dK/dV accumulators)
   int b, h;
+  int hk;                     // K/V head: h, or h / kv_group with grouped-query attention
 };
 
 __device__ __forceinline__ SegInfo seg_info(const ha_attn_params& p, int seg) {
@@ -17,7 +19,18 @@ __device__ __forceinline__ SegInfo seg_info(const ha_attn_params& p, int seg) {
   s.h = bh - s.b * p.H;
   s.q_row0 = (long long)part * p.span + p.q_off;
   s.k_row0 = (long long)part * p.span + p.k_off;
+  const int g = p.kv_group > 1 ? p.kv_group : 1;
+  s.hk = s.h / g;
+  s.khead0 = ((long long)s.b * (p.H / g) + s.hk) * p.n;
   return s;
+}
+
+// Index of segment `seg` on the key side (rows of k_idx / sample_idx): the same segment of the K/V head.
+__device__ __forceinline__ long long kseg_of(const ha_attn_params& p, long long seg) {
+  if (p.kv_group <= 1) return seg;
+  const long long bh = seg / p.segs_per_head, part = seg - bh * p.segs_per_head;
+  const long long b = bh / p.H, h = bh - b * p.H;
+  return (b * (p.H / p.kv_group) + h / p.kv_group) * p.segs_per_head + part;
 }
 
 // Block window of a 128-row tile t of one side (hyper mode, m rows per side, W = block size rounded up to tiles):

@@ -40,10 +40,10 @@ __device__ __forceinline__ int fwd_key_row(const ha_attn_params& p, int seg, con
   if (j < n_blk) {
     int pos = w.first + j;
     if (pos >= p.m_k) pos -= p.m_k;
-    return p.k_idx[(long long)seg * p.m_k + pos];
+    return p.k_idx[kseg_of(p, seg) * p.m_k + pos];
   }
   const int s = j - n_blk;
-  return p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + s] : s;
+  return p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + s] : s;
 }
 
 // weighted sampling: is slot s dropped for sorted query tile t of this segment?
@@ -66,8 +66,8 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_fwd_kernel(const ha
   const T* qp = (const T*)p.q + si.b * p.q_sb + si.h * p.q_sh + (si.q_row0 + qrow) * p.q_sn;
   for (int e = lane; e < p.d; e += 32) sq[warp][e] = to_f32<T>(qp[e]);
   __syncwarp();
-  const T* kbase = (const T*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
-  const T* vbase = (const T*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn;
+  const T* kbase = (const T*)p.k + si.b * p.k_sb + si.hk * p.k_sh + si.k_row0 * p.k_sn;
+  const T* vbase = (const T*)p.v + si.b * p.v_sb + si.hk * p.v_sh + si.k_row0 * p.v_sn;
 
   Window w{0, 0};
   int n_blk = 0, n_keys;
@@ -212,10 +212,10 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_bwd_kernel(const ha
     const int first = (p.flags & HA_FLAG_CAUSAL) ? kk : 0;
     ql = {p.m_q - first, 1, first, 0, 0};
   } else if (phase == 1) {
-    krow = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + kk] : kk;
+    krow = p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + kk] : kk;
     ql = {p.m_q, p.sample_logw ? 0 : 1, 0, 0, 0};   // weighted: by sorted position, so that j / 128 is the query tile
   } else {
-    krow = p.k_idx[(long long)seg * p.m_k + kk];
+    krow = p.k_idx[kseg_of(p, seg) * p.m_k + kk];
     const int t = kk / TILE;
     const bool smooth = p.flags & HA_FLAG_SMOOTH;
     if (!smooth || (p.flags & HA_FLAG_BWD_REF_SMOOTH)) {
@@ -231,8 +231,8 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_bwd_kernel(const ha
   const int j_begin = chunk * QCHUNK, j_end = min(ql.len, j_begin + QCHUNK);
   if (j_begin >= j_end) return;
 
-  const T* kp = (const T*)p.k + si.b * p.k_sb + si.h * p.k_sh + (si.k_row0 + krow) * p.k_sn;
-  const T* vp = (const T*)p.v + si.b * p.v_sb + si.h * p.v_sh + (si.k_row0 + krow) * p.v_sn;
+  const T* kp = (const T*)p.k + si.b * p.k_sb + si.hk * p.k_sh + (si.k_row0 + krow) * p.k_sn;
+  const T* vp = (const T*)p.v + si.b * p.v_sb + si.hk * p.v_sh + (si.k_row0 + krow) * p.v_sn;
   for (int e = lane; e < p.d; e += 32) sk[warp][e] = to_f32<T>(kp[e]);
   for (int e = lane; e < p.dv; e += 32) sv[warp][e] = to_f32<T>(vp[e]);
   __syncwarp();
@@ -282,8 +282,8 @@ __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_bwd_kernel(const ha
       }
     }
   }
-  float* dkp = p.dk_acc + (head0 + si.k_row0 + krow) * p.d;
-  float* dvp = p.dv_acc + (head0 + si.k_row0 + krow) * p.dv;
+  float* dkp = p.dk_acc + (si.khead0 + si.k_row0 + krow) * p.d;
+  float* dvp = p.dv_acc + (si.khead0 + si.k_row0 + krow) * p.dv;
 #pragma unroll
   for (int i = 0; i < VR; ++i) {
     const int e = lane + 32 * i;

@@ -195,8 +195,8 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
     // block size 256, plain windows: key tiles 2b, 2b+1 and query tiles 2b, 2b+1 form four pairs
     it.paired = true;
     it.k_tile = 2 * item;
-    it.krow = p.k_idx[(long long)seg * p.m_k + it.k_tile * TILE + tid];
-    it.krow2 = p.k_idx[(long long)seg * p.m_k + (it.k_tile + 1) * TILE + tid];
+    it.krow = p.k_idx[kseg_of(p, seg) * p.m_k + it.k_tile * TILE + tid];
+    it.krow2 = p.k_idx[kseg_of(p, seg) * p.m_k + (it.k_tile + 1) * TILE + tid];
     it.q_sorted = true;
     it.q_pos0 = it.k_tile * TILE;
     it.qt_count = 4;
@@ -204,12 +204,12 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
       // ... and the two sampled key tiles against the same two query tiles: pairs 4..7
       it.fused = true;
       it.qt_count = 8;
-      it.srow0 = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + tid] : tid;
-      it.srow1 = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + TILE + tid] : TILE + tid;
+      it.srow0 = p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + tid] : tid;
+      it.srow1 = p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + TILE + tid] : TILE + tid;
     }
   } else if (hyper && item < items_blk) {
     it.k_tile = item;
-    it.krow = p.k_idx[(long long)seg * p.m_k + it.k_tile * TILE + tid];
+    it.krow = p.k_idx[kseg_of(p, seg) * p.m_k + it.k_tile * TILE + tid];
     const int bs = (p.block_size + TILE - 1) / TILE;
     const Window w = block_window(it.k_tile, bs, p.m_q, p.flags & HA_FLAG_SMOOTH);
     it.q_sorted = true;
@@ -229,7 +229,7 @@ __device__ __forceinline__ BwdItem bwd_decode(const ha_attn_params& p, int item,
       z = i2 - it.k_tile * n_chunks;
     }
     const int kr = it.k_tile * TILE + tid;
-    if (hyper) it.krow = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + kr] : kr;
+    if (hyper) it.krow = p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + kr] : kr;
     else it.krow = kr < p.m_k ? kr : -1;
     it.qt_first = z * BWD_CHUNK;
     if (!hyper && (p.flags & HA_FLAG_CAUSAL)) it.qt_first = max(it.qt_first, it.k_tile);
@@ -343,8 +343,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     const bool go = wk.valid && wk.me.qt_count > 0;
     const uint16_t* qb = (const uint16_t*)p.q + wk.si.b * p.q_sb + wk.si.h * p.q_sh + wk.si.q_row0 * p.q_sn;
     const uint16_t* gb = (const uint16_t*)p.d_o + wk.si.b * p.do_sb + wk.si.h * p.do_sh + wk.si.q_row0 * p.do_sn;
-    const uint16_t* kb = (const uint16_t*)p.k + wk.si.b * p.k_sb + wk.si.h * p.k_sh + wk.si.k_row0 * p.k_sn;
-    const uint16_t* vb = (const uint16_t*)p.v + wk.si.b * p.v_sb + wk.si.h * p.v_sh + wk.si.k_row0 * p.v_sn;
+    const uint16_t* kb = (const uint16_t*)p.k + wk.si.b * p.k_sb + wk.si.hk * p.k_sh + wk.si.k_row0 * p.k_sn;
+    const uint16_t* vb = (const uint16_t*)p.v + wk.si.b * p.v_sb + wk.si.hk * p.v_sh + wk.si.k_row0 * p.v_sn;
     if (go) {
       if (wg == 0) {
         bwd_gather_tile<D>(s_base + Cfg::OFF_K, kb, p.k_sn, wk.me.krow, qwarp, lane);
@@ -512,8 +512,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   auto drain_kv = [&](int kr, int tile, bool sampled_tile) {
     uint8_t* stg = smem + Cfg::OFF_STG + wg * Cfg::STG_HALF;
     if (p.dk_out == nullptr) {
-      float* dk_base = p.dk_acc + (head0 + si.k_row0) * D;
-      float* dv_base = p.dv_acc + (head0 + si.k_row0) * DV;
+      float* dk_base = p.dk_acc + (si.khead0 + si.k_row0) * D;
+      float* dv_base = p.dv_acc + (si.khead0 + si.k_row0) * DV;
       if (p.flags & HA_FLAG_BWD_KV_INIT) {   // (exact attention only) this item is the only writer of its key rows: store, nothing to add to
         reduce_rows<DV / 2, 1>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, kr, row);
         reduce_rows<D / 2, 1>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr, row);
@@ -528,8 +528,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       store_rows<T, D / 2>(tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, kr);
     } else {
       const int slot = tile * TILE + row;
-      float* dk_base = p.dk_sacc + (long long)seg * p.sample_size * D;
-      float* dv_base = p.dv_sacc + (long long)seg * p.sample_size * DV;
+      float* dk_base = p.dk_sacc + kseg_of(p, seg) * p.sample_size * D;
+      float* dv_base = p.dv_sacc + kseg_of(p, seg) * p.sample_size * DV;
       reduce_rows<DV / 2>(stg, tDV + lane_sel + wg * (DV / 2), dv_base + wg * (DV / 2), DV, slot, row);
       reduce_rows<D / 2>(stg, tDK + lane_sel + wg * (D / 2), dk_base + wg * (D / 2), D, slot, row);
     }
@@ -591,8 +591,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       if (fused && (jj == 2 || jj == 4)) {
         // the key buffer whose tile is through (A at pair 2, B at pair 4) takes a sampled tile, needed two pairs later
         const int sr = jj == 2 ? me.srow0 : me.srow1;
-        const uint16_t* kb = (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
-        const uint16_t* vb = (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn;
+        const uint16_t* kb = (const uint16_t*)p.k + si.b * p.k_sb + si.hk * p.k_sh + si.k_row0 * p.k_sn;
+        const uint16_t* vb = (const uint16_t*)p.v + si.b * p.v_sb + si.hk * p.v_sh + si.k_row0 * p.v_sn;
         if (wg == 0) bwd_gather_tile<D>(s_base + (jj == 2 ? Cfg::OFF_K : Cfg::OFF_K2), kb, p.k_sn, sr, qwarp, lane);
         else bwd_gather_tile<DV>(s_base + (jj == 2 ? Cfg::OFF_V : Cfg::OFF_V2), vb, p.v_sn, sr, qwarp, lane);
       }

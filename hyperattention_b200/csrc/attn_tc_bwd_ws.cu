@@ -278,9 +278,9 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
       const int qrow0 = p.q_idx[(long long)seg * p.m_q + (2 * blk) * TILE + row];
       const int qrow1 = p.q_idx[(long long)seg * p.m_q + (2 * blk + 1) * TILE + row];
       auto key_row = [&](int x) -> int {
-        if (x < 2) return p.k_idx[(long long)seg * p.m_k + (2 * blk + x) * TILE + row];
+        if (x < 2) return p.k_idx[kseg_of(p, seg) * p.m_k + (2 * blk + x) * TILE + row];
         const int s = (x - 2) * TILE + row;
-        return p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + s] : s;
+        return p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + s] : s;
       };
       auto drain_dq = [&](int y) -> bool {
         HA_T_MARK(1)
@@ -308,11 +308,11 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
         // window tiles: the row's complete block part, stored once (typed) / added (accumulators); sampled tiles: this
         // block's share of the row's sum, reduced into the slot buffers (typed outputs) / the accumulators
         const bool typed = kv_direct && !sampled;
-        const long long r = head0 + si.k_row0 + krow;
+        const long long r = si.khead0 + si.k_row0 + krow;
         float* acc_k = nullptr;
         float* acc_v = nullptr;
         if (kv_direct && sampled) {
-          const long long slot = (long long)seg * p.sample_size + (x - 2) * TILE + row;
+          const long long slot = kseg_of(p, seg) * p.sample_size + (x - 2) * TILE + row;
           acc_k = p.dk_sacc + slot * D;
           acc_v = p.dv_sacc + slot * DV;
         } else if (!kv_direct) {
@@ -359,10 +359,10 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int rr = q * 32 + lane;
-            if (x < 2) dst[q] = p.k_idx[(long long)seg * p.m_k + (2 * blk + x) * TILE + rr];
+            if (x < 2) dst[q] = p.k_idx[kseg_of(p, seg) * p.m_k + (2 * blk + x) * TILE + rr];
             else {
               const int s = (x - 2) * TILE + rr;
-              dst[q] = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + s] : s;
+              dst[q] = p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + s] : s;
             }
           }
         };
@@ -371,8 +371,8 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
           const int seg = item / blocks_per_seg, blk = item - seg * blocks_per_seg;
           const SegInfo si = seg_info(p, seg);
-          const uint16_t* base = is_v ? (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn
-                                      : (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
+          const uint16_t* base = is_v ? (const uint16_t*)p.v + si.b * p.v_sb + si.hk * p.v_sh + si.k_row0 * p.v_sn
+                                      : (const uint16_t*)p.k + si.b * p.k_sb + si.hk * p.k_sh + si.k_row0 * p.k_sn;
           const int64_t sn = is_v ? p.v_sn : p.k_sn;
           for (int x = 0; x < nX && ok; ++x, ++xg) {
             // the next tile's row indices (the next item's first tile after this item's last) travel during the wait
@@ -383,8 +383,8 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
             // is limited, meet L2 latency rather than DRAM latency
             if (x + 1 < 2 || x + 1 == nX) {       // window tiles only: the sampled rows are shared by the whole segment
               const SegInfo nsi = x + 1 < nX ? si : seg_info(p, (item + (int)gridDim.x) / blocks_per_seg);
-              const uint16_t* nbase = is_v ? (const uint16_t*)p.v + nsi.b * p.v_sb + nsi.h * p.v_sh + nsi.k_row0 * p.v_sn
-                                           : (const uint16_t*)p.k + nsi.b * p.k_sb + nsi.h * p.k_sh + nsi.k_row0 * p.k_sn;
+              const uint16_t* nbase = is_v ? (const uint16_t*)p.v + nsi.b * p.v_sb + nsi.hk * p.v_sh + nsi.k_row0 * p.v_sn
+                                           : (const uint16_t*)p.k + nsi.b * p.k_sb + nsi.hk * p.k_sh + nsi.k_row0 * p.k_sn;
 #pragma unroll
               for (int q = 0; q < 4; ++q)
                 if (knext[q] >= 0) prefetch_l2(nbase + (int64_t)knext[q] * sn);

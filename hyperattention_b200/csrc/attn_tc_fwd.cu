@@ -141,15 +141,15 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
     if (j < tl.n_blk) {
       int pos = tl.w.first + j * TILE + tid;
       if (pos >= p.m_k) pos -= p.m_k;
-      return p.k_idx[(long long)seg * p.m_k + pos];
+      return p.k_idx[kseg_of(p, seg) * p.m_k + pos];
     }
     const int s = (j - tl.n_blk) * TILE + tid;
-    return p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + s] : s;
+    return p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + s] : s;
   };
 
   const uint16_t* qbase = (const uint16_t*)p.q + si.b * p.q_sb + si.h * p.q_sh + si.q_row0 * p.q_sn;
-  const uint16_t* kbase = (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
-  const uint16_t* vbase = (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn;
+  const uint16_t* kbase = (const uint16_t*)p.k + si.b * p.k_sb + si.hk * p.k_sh + si.k_row0 * p.k_sn;
+  const uint16_t* vbase = (const uint16_t*)p.v + si.b * p.v_sb + si.hk * p.v_sh + si.k_row0 * p.v_sn;
   uint16_t* obase = (uint16_t*)p.o + si.b * p.o_sb + si.h * p.o_sh + si.q_row0 * p.o_sn;
   const bool merge = p.flags & HA_FLAG_MERGE;
 
@@ -184,9 +184,9 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
         if (i < pn_blk) {
           int pos = pw.first + i * TILE + tid;
           if (pos >= p.m_k) pos -= p.m_k;
-          pf_k[i] = p.k_idx[(long long)pseg * p.m_k + pos];
+          pf_k[i] = p.k_idx[kseg_of(p, pseg) * p.m_k + pos];
         } else if (p.sample_idx && (i - pn_blk) * TILE < p.sample_size) {
-          pf_k[i] = p.sample_idx[(long long)pseg * p.sample_size + (i - pn_blk) * TILE + tid];
+          pf_k[i] = p.sample_idx[kseg_of(p, pseg) * p.sample_size + (i - pn_blk) * TILE + tid];
         }
       }
     }
@@ -380,8 +380,8 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
     krow_next = krow_after;
     if (j == 0 && pf_q >= 0) {
       const uint16_t* pq = (const uint16_t*)p.q + pf_si.b * p.q_sb + pf_si.h * p.q_sh + (pf_si.q_row0 + pf_q) * p.q_sn;
-      const uint16_t* pk = (const uint16_t*)p.k + pf_si.b * p.k_sb + pf_si.h * p.k_sh + pf_si.k_row0 * p.k_sn;
-      const uint16_t* pv = (const uint16_t*)p.v + pf_si.b * p.v_sb + pf_si.h * p.v_sh + pf_si.k_row0 * p.v_sn;
+      const uint16_t* pk = (const uint16_t*)p.k + pf_si.b * p.k_sb + pf_si.hk * p.k_sh + pf_si.k_row0 * p.k_sn;
+      const uint16_t* pv = (const uint16_t*)p.v + pf_si.b * p.v_sb + pf_si.hk * p.v_sh + pf_si.k_row0 * p.v_sn;
       prefetch_l2(pq);
       if (D > 64) prefetch_l2(pq + 64);
       if (merge) {

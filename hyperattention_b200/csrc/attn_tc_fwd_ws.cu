@@ -322,10 +322,10 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int rr = q * 32 + lane;
-          if (j < n_blk) dst[q] = p.k_idx[(long long)seg * p.m_k + (2 * blk + j) * TILE + rr];
+          if (j < n_blk) dst[q] = p.k_idx[kseg_of(p, seg) * p.m_k + (2 * blk + j) * TILE + rr];
           else {
             const int s = (j - n_blk) * TILE + rr;
-            dst[q] = p.sample_idx ? p.sample_idx[(long long)seg * p.sample_size + s] : s;
+            dst[q] = p.sample_idx ? p.sample_idx[kseg_of(p, seg) * p.sample_size + s] : s;
           }
         }
       };
@@ -334,8 +334,8 @@ __global__ void __launch_bounds__(ws::THREADS, 1) attn_tc_fwd_ws_kernel(const ha
       for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
         const int seg = item / blocks_per_seg, blk = item - seg * blocks_per_seg;
         const SegInfo si = seg_info(p, seg);
-        const uint16_t* base = is_v ? (const uint16_t*)p.v + si.b * p.v_sb + si.h * p.v_sh + si.k_row0 * p.v_sn
-                                    : (const uint16_t*)p.k + si.b * p.k_sb + si.h * p.k_sh + si.k_row0 * p.k_sn;
+        const uint16_t* base = is_v ? (const uint16_t*)p.v + si.b * p.v_sb + si.hk * p.v_sh + si.k_row0 * p.v_sn
+                                    : (const uint16_t*)p.k + si.b * p.k_sb + si.hk * p.k_sh + si.k_row0 * p.k_sn;
         const int64_t sn = is_v ? p.v_sn : p.k_sn;
         for (int j = 0; j < n_tiles && ok; ++j, ++kv_t) {
           const int stage = kv_t % KV_STAGES;

@@ -44,6 +44,8 @@ static SideStream* side_stream() {
 
 struct CausalPlan {
   long long rows;          // B*H*n
+  long long rows_k;        // B*(H / kv_group)*n: rows of k, v, dk, dv
+  int Hk;                  // K/V heads
   long long idx_bytes;     // one depth's q_idx or k_idx
   long long part_o_bytes, part_lse_bytes;
   long long sort_ws;       // largest sort workspace over the depths
@@ -62,7 +64,10 @@ static int make_plan(const ha_causal_params& p, CausalPlan& pl) {
   if (pl.leaf % TILE != 0) return HA_ERR_INVALID;
   const bool deepest_is_exact = p.min_seq_len > pl.leaf;
   if (!(deepest_is_exact && p.levels == 1) && p.sample_size > (deepest_is_exact ? 2 * pl.leaf : pl.leaf)) return HA_ERR_INVALID;
+  if (p.kv_group < 0 || (p.kv_group > 1 && p.H % p.kv_group != 0)) return HA_ERR_INVALID;
+  pl.Hk = p.kv_group > 1 ? p.H / p.kv_group : p.H;
   pl.rows = (long long)p.B * p.H * p.n;
+  pl.rows_k = (long long)p.B * pl.Hk * p.n;
   pl.idx_bytes = pl.rows / 2 * 4;
   pl.part_o_bytes = pl.rows * p.dv * dtype_size(p.dtype);
   pl.part_lse_bytes = pl.rows * 4;
@@ -164,11 +169,13 @@ static void fill_attn(const ha_causal_params& p, ha_attn_params& a) {
   a.block_size = p.block_size; a.sample_size = p.sample_size; a.scale = p.scale;
   a.q = p.q; a.k = p.k; a.v = p.v;
   a.q_sn = p.d; a.q_sh = (int64_t)p.n * p.d; a.q_sb = a.q_sh * p.H;
-  a.k_sn = p.d; a.k_sh = a.q_sh; a.k_sb = a.q_sb;
-  a.v_sn = p.dv; a.v_sh = (int64_t)p.n * p.dv; a.v_sb = a.v_sh * p.H;
-  a.o = p.o; a.o_sn = p.dv; a.o_sh = a.v_sh; a.o_sb = a.v_sb;
+  const int Hk = p.kv_group > 1 ? p.H / p.kv_group : p.H;
+  a.kv_group = p.kv_group;
+  a.k_sn = p.d; a.k_sh = a.q_sh; a.k_sb = a.k_sh * Hk;
+  a.v_sn = p.dv; a.v_sh = (int64_t)p.n * p.dv; a.v_sb = a.v_sh * Hk;
+  a.o = p.o; a.o_sn = p.dv; a.o_sh = a.v_sh; a.o_sb = a.o_sh * p.H;
   a.lse = p.lse;
-  a.d_o = p.d_o; a.do_sn = p.dv; a.do_sh = a.v_sh; a.do_sb = a.v_sb;
+  a.d_o = p.d_o; a.do_sn = p.dv; a.do_sh = a.v_sh; a.do_sb = a.o_sb;
   a.status = p.status;
   a.status_host = p.status_host;
 }
@@ -194,7 +201,7 @@ int64_t ha_causal_scratch_bytes(const ha_causal_params* p, int32_t backward) {
   CausalPlan pl;
   if (!p || make_plan(*p, pl) != HA_OK) return -1;
   if (!backward) return 2 * align256(pl.rows * 4) + align256(pl.sort_ws);
-  return align256(pl.rows * p->d * 4) * 2 + align256(pl.rows * p->dv * 4) + align256(pl.rows * 4 * (p->levels + 1));
+  return align256(pl.rows * p->d * 4) + align256(pl.rows_k * p->d * 4) + align256(pl.rows_k * p->dv * 4) + align256(pl.rows * 4 * (p->levels + 1));
 }
 
 int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
@@ -214,7 +221,7 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
   const int64_t sn = p.d, sh = (int64_t)p.n * p.d, sb = sh * p.H;
   rc = ha_lsh_hash(p.q, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes_q, stream);
   if (rc != HA_OK) return rc;
-  rc = ha_lsh_hash(p.k, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes_k, stream);
+  rc = ha_lsh_hash(p.k, sh * pl.Hk, sh, sn, p.B, pl.Hk, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes_k, stream);
   if (rc != HA_OK) return rc;
 
   // The sorts of every depth depend on the codes only: they run on a side stream (forked here, joined before the first
@@ -235,7 +242,7 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
     const int span = p.n >> l, m = span / 2;
     sort_rc = ha_seg_sort(codes_q, p.B * p.H, p.n, span, m, m, p.lsh_bits, sv.q_idx(l), sort_ws, pl.sort_ws, sort_stream);
     if (sort_rc == HA_OK)
-      sort_rc = ha_seg_sort(codes_k, p.B * p.H, p.n, span, 0, m, p.lsh_bits, sv.k_idx(l), sort_ws, pl.sort_ws, sort_stream);
+      sort_rc = ha_seg_sort(codes_k, p.B * pl.Hk, p.n, span, 0, m, p.lsh_bits, sv.k_idx(l), sort_ws, pl.sort_ws, sort_stream);
   }
   if (side) {   // joined in every case, so that the caller's stream also orders after whatever the side stream holds
     HA_CUDA_OK(cudaEventRecord(side->join, side->stream), "ha_causal_fwd join");
@@ -286,8 +293,8 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   uint8_t* s = (uint8_t*)p.scratch;
   float* dq_acc = (float*)s;                 s += align256(pl.rows * p.d * 4);
-  float* dk_acc = (float*)s;                 s += align256(pl.rows * p.d * 4);
-  float* dv_acc = (float*)s;                 s += align256(pl.rows * p.dv * 4);
+  float* dk_acc = (float*)s;                 s += align256(pl.rows_k * p.d * 4);
+  float* dv_acc = (float*)s;                 s += align256(pl.rows_k * p.dv * 4);
   float* delta = (float*)s;
   ha_attn_params a;
   fill_attn(p, a);
@@ -301,12 +308,12 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
     probe.flags = HA_FLAG_CAUSAL | (p.flags & HA_FLAG_FORCE_SIMT);
     probe.segs_per_head = 1 << p.levels;
     probe.span = pl.leaf; probe.m_q = pl.leaf; probe.m_k = pl.leaf;
-    kv_init = pl.leaf <= 16 * TILE && !(p.flags & HA_FLAG_FORCE_SIMT) && tc_bwd_supported(probe);
+    kv_init = pl.leaf <= 16 * TILE && !(p.flags & HA_FLAG_FORCE_SIMT) && p.kv_group <= 1 && tc_bwd_supported(probe);
   }
   HA_CUDA_OK(cudaMemsetAsync(dq_acc, 0, pl.rows * p.d * 4, st), "ha_causal_bwd memset");
   if (!kv_init) {
-    HA_CUDA_OK(cudaMemsetAsync(dk_acc, 0, pl.rows * p.d * 4, st), "ha_causal_bwd memset");
-    HA_CUDA_OK(cudaMemsetAsync(dv_acc, 0, pl.rows * p.dv * 4, st), "ha_causal_bwd memset");
+    HA_CUDA_OK(cudaMemsetAsync(dk_acc, 0, pl.rows_k * p.d * 4, st), "ha_causal_bwd memset");
+    HA_CUDA_OK(cudaMemsetAsync(dv_acc, 0, pl.rows_k * p.dv * 4, st), "ha_causal_bwd memset");
   }
   // reference gradient convention: every part uses sum(o_part * dO) of its own output (its d(lse) is dropped);
   // exact convention: sum(o * dO) of the merged output, computed once
@@ -358,9 +365,9 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
   }
   rc = ha_cast_from_f32(dq_acc, p.dq, pl.rows * p.d, p.dtype, stream);
   if (rc != HA_OK) return rc;
-  rc = ha_cast_from_f32(dk_acc, p.dk, pl.rows * p.d, p.dtype, stream);
+  rc = ha_cast_from_f32(dk_acc, p.dk, pl.rows_k * p.d, p.dtype, stream);
   if (rc != HA_OK) return rc;
-  return ha_cast_from_f32(dv_acc, p.dv_out, pl.rows * p.dv, p.dtype, stream);
+  return ha_cast_from_f32(dv_acc, p.dv_out, pl.rows_k * p.dv, p.dtype, stream);
 }
 
 
@@ -372,12 +379,14 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
  * saved: q_idx | k_idx.  scratch: forward = codes of q and k + sort workspace; backward = delta + slot buffers / fp32
  * accumulators as the backward kernel needs them.
  * --------------------------------------------------------------------------------------------------------------- */
-static int noncausal_check(const ha_causal_params& p, long long& rows) {
+static int noncausal_check(const ha_causal_params& p, long long& rows, long long& rows_k) {
   if (p.dtype != HA_BF16 && p.dtype != HA_FP16 && p.dtype != HA_FP32) return HA_ERR_DTYPE;
   if (p.B <= 0 || p.H <= 0 || p.n <= 0 || p.d <= 0 || p.dv <= 0 || p.d > 256 || p.dv > 256) return HA_ERR_INVALID;
   if (p.lsh_bits < 1 || p.lsh_bits > 16 || p.n % TILE != 0) return HA_ERR_INVALID;
   if (p.sample_size < 0 || p.sample_size % TILE != 0 || p.sample_size > p.n || p.block_size < 1) return HA_ERR_INVALID;
+  if (p.kv_group < 0 || (p.kv_group > 1 && p.H % p.kv_group != 0)) return HA_ERR_INVALID;
   rows = (long long)p.B * p.H * p.n;
+  rows_k = p.kv_group > 1 ? rows / p.kv_group : rows;
   return HA_OK;
 }
 
@@ -402,29 +411,29 @@ static int noncausal_bwd_level(const ha_causal_params& p, long long rows) {
 }
 
 int64_t ha_noncausal_saved_bytes(const ha_causal_params* p) {
-  long long rows;
-  if (!p || noncausal_check(*p, rows) != HA_OK) return -1;
+  long long rows, rows_k;
+  if (!p || noncausal_check(*p, rows, rows_k) != HA_OK) return -1;
   return 2 * align256(rows * 4);
 }
 
 int64_t ha_noncausal_scratch_bytes(const ha_causal_params* p, int32_t backward) {
-  long long rows;
-  if (!p || noncausal_check(*p, rows) != HA_OK) return -1;
+  long long rows, rows_k;
+  if (!p || noncausal_check(*p, rows, rows_k) != HA_OK) return -1;
   if (!backward) return 2 * align256(rows * 4) + align256(ha_seg_sort_workspace_bytes(2 * p->B * p->H, p->n, p->n, p->n, p->lsh_bits));
   const int level = noncausal_bwd_level(*p, rows);
   const long long sacc = align256((long long)p->B * p->H * p->sample_size * (p->d + p->dv) * 4);
   long long bytes = align256(rows * 4);
   if (level == 2) bytes += sacc;
   else if (level == 1) bytes += sacc + align256(rows * p->d * 4);
-  else bytes += 2 * align256(rows * p->d * 4) + align256(rows * p->dv * 4);
+  else bytes += align256(rows * p->d * 4) + align256(rows_k * p->d * 4) + align256(rows_k * p->dv * 4);
   return bytes;
 }
 
 int ha_noncausal_fwd(const ha_causal_params* pp, void* stream) {
   if (!pp) return HA_ERR_INVALID;
   const ha_causal_params& p = *pp;
-  long long rows;
-  int rc = noncausal_check(p, rows);
+  long long rows, rows_k;
+  int rc = noncausal_check(p, rows, rows_k);
   if (rc != HA_OK) return rc;
   if (!p.q || !p.k || !p.v || !p.o || !p.lse || !p.proj) return HA_ERR_INVALID;
   if (!p.saved || p.saved_bytes < ha_noncausal_saved_bytes(pp)) return HA_ERR_WORKSPACE;
@@ -437,14 +446,15 @@ int ha_noncausal_fwd(const ha_causal_params* pp, void* stream) {
   const int64_t sn = p.d, sh = (int64_t)p.n * p.d, sb = sh * p.H;
   rc = ha_lsh_hash(p.q, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes, stream);
   if (rc != HA_OK) return rc;
-  rc = ha_lsh_hash(p.k, sb, sh, sn, p.B, p.H, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes + rows, stream);
+  const int Hk = p.kv_group > 1 ? p.H / p.kv_group : p.H;
+  rc = ha_lsh_hash(p.k, sh * Hk, sh, sn, p.B, Hk, p.n, p.d, p.dtype, p.proj, p.lsh_bits, codes + rows, stream);
   if (rc != HA_OK) return rc;
-  if (align256(rows * 4) == rows * 4) {
+  if (align256(rows * 4) == rows * 4 && Hk == p.H) {
     rc = ha_seg_sort(codes, 2 * p.B * p.H, p.n, p.n, 0, p.n, p.lsh_bits, (int32_t*)p.saved, sort_ws, sort_ws_bytes, stream);
   } else {
     rc = ha_seg_sort(codes, p.B * p.H, p.n, p.n, 0, p.n, p.lsh_bits, (int32_t*)p.saved, sort_ws, sort_ws_bytes, stream);
     if (rc == HA_OK)
-      rc = ha_seg_sort(codes + rows, p.B * p.H, p.n, p.n, 0, p.n, p.lsh_bits, (int32_t*)((uint8_t*)p.saved + align256(rows * 4)), sort_ws,
+      rc = ha_seg_sort(codes + rows, p.B * Hk, p.n, p.n, 0, p.n, p.lsh_bits, (int32_t*)((uint8_t*)p.saved + align256(rows * 4)), sort_ws,
                        sort_ws_bytes, stream);
   }
   if (rc != HA_OK) return rc;
@@ -456,8 +466,8 @@ int ha_noncausal_fwd(const ha_causal_params* pp, void* stream) {
 int ha_noncausal_bwd(const ha_causal_params* pp, void* stream) {
   if (!pp) return HA_ERR_INVALID;
   const ha_causal_params& p = *pp;
-  long long rows;
-  int rc = noncausal_check(p, rows);
+  long long rows, rows_k;
+  int rc = noncausal_check(p, rows, rows_k);
   if (rc != HA_OK) return rc;
   if (!p.q || !p.k || !p.v || !p.o || !p.lse || !p.d_o || !p.dq || !p.dk || !p.dv_out) return HA_ERR_INVALID;
   if (!p.saved || p.saved_bytes < ha_noncausal_saved_bytes(pp)) return HA_ERR_WORKSPACE;
@@ -494,24 +504,24 @@ int ha_noncausal_bwd(const ha_causal_params* pp, void* stream) {
     return rc;
   }
   a.dq_acc = (float*)s;                      s += align256(rows * p.d * 4);
-  a.dk_acc = (float*)s;                      s += align256(rows * p.d * 4);
+  a.dk_acc = (float*)s;                      s += align256(rows_k * p.d * 4);
   a.dv_acc = (float*)s;
   HA_CUDA_OK(cudaMemsetAsync(a.dq_acc, 0, rows * p.d * 4, st), "ha_noncausal_bwd memset");
-  HA_CUDA_OK(cudaMemsetAsync(a.dk_acc, 0, rows * p.d * 4, st), "ha_noncausal_bwd memset");
-  HA_CUDA_OK(cudaMemsetAsync(a.dv_acc, 0, rows * p.dv * 4, st), "ha_noncausal_bwd memset");
+  HA_CUDA_OK(cudaMemsetAsync(a.dk_acc, 0, rows_k * p.d * 4, st), "ha_noncausal_bwd memset");
+  HA_CUDA_OK(cudaMemsetAsync(a.dv_acc, 0, rows_k * p.dv * 4, st), "ha_noncausal_bwd memset");
   rc = ha_attn_bwd(&a, stream);
   if (rc != HA_OK) return rc;
   if (p.dtype == HA_FP32) {
     HA_CUDA_OK(cudaMemcpyAsync(p.dq, a.dq_acc, rows * p.d * 4, cudaMemcpyDeviceToDevice, st), "ha_noncausal_bwd copy");
-    HA_CUDA_OK(cudaMemcpyAsync(p.dk, a.dk_acc, rows * p.d * 4, cudaMemcpyDeviceToDevice, st), "ha_noncausal_bwd copy");
-    HA_CUDA_OK(cudaMemcpyAsync(p.dv_out, a.dv_acc, rows * p.dv * 4, cudaMemcpyDeviceToDevice, st), "ha_noncausal_bwd copy");
+    HA_CUDA_OK(cudaMemcpyAsync(p.dk, a.dk_acc, rows_k * p.d * 4, cudaMemcpyDeviceToDevice, st), "ha_noncausal_bwd copy");
+    HA_CUDA_OK(cudaMemcpyAsync(p.dv_out, a.dv_acc, rows_k * p.dv * 4, cudaMemcpyDeviceToDevice, st), "ha_noncausal_bwd copy");
     return HA_OK;
   }
   rc = ha_cast_from_f32(a.dq_acc, p.dq, rows * p.d, p.dtype, stream);
   if (rc != HA_OK) return rc;
-  rc = ha_cast_from_f32(a.dk_acc, p.dk, rows * p.d, p.dtype, stream);
+  rc = ha_cast_from_f32(a.dk_acc, p.dk, rows_k * p.d, p.dtype, stream);
   if (rc != HA_OK) return rc;
-  return ha_cast_from_f32(a.dv_acc, p.dv_out, rows * p.dv, p.dtype, stream);
+  return ha_cast_from_f32(a.dv_acc, p.dv_out, rows_k * p.dv, p.dtype, stream);
 }
 
 }  // extern "C"

@@ -60,6 +60,10 @@ class FastCoreAttention(torch.nn.Module):
             self.coeff = self.layer_number
             self.norm_factor *= self.coeff
         self.attention_dropout = torch.nn.Dropout(config.attention_dropout)
+        # grouped_kv=True: the caller may hand over K/V with fewer heads than Q (multi-query / grouped-query models); K is then
+        # hashed and sorted once per K/V head and never expanded.  False (default): heads already expanded, as the
+        # reference's callers do (chatglm_fast_attention.py:53-58).
+        self.grouped_kv = bool(kwargs.get('grouped_kv', False))
         self.attn_method = kwargs.get('attn_method')
         if self.attn_method != 'hyper':
             raise NotImplementedError("Invalid attn_method option")
@@ -171,8 +175,9 @@ class SelfAttention(torch.nn.Module):
         rep = self.heads // self.groups
         # multi-query: every key/value group serves heads/groups query heads; expanded before the core, as the
         # attention core of the original model expects equal head counts
-        k = k.unsqueeze(3).expand(-1, -1, -1, rep, -1).reshape(sq, b, self.heads, self.hn)
-        v = v.unsqueeze(3).expand(-1, -1, -1, rep, -1).reshape(sq, b, self.heads, self.hn)
+        if not getattr(self.core_attention, 'grouped_kv', False):
+            k = k.unsqueeze(3).expand(-1, -1, -1, rep, -1).reshape(sq, b, self.heads, self.hn)
+            v = v.unsqueeze(3).expand(-1, -1, -1, rep, -1).reshape(sq, b, self.heads, self.hn)
         return self.dense(self.core_attention(q, k, v, None))
 
 

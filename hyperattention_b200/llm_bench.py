@@ -45,13 +45,20 @@ def main():
     patch_attention_layers(model, 'chatglm2-6b-32k', 'last', a.patch_layers, num_total_layers=a.layers, attn_method='hyper',
                            lsh_num_projs=8, block_size=256, sample_size=256, min_seq_len=2048, smooth_block=False)
     ms_hyper, logits_hyper = timed(lambda: model(ids))
+    # the same patched model with K/V handed over un-expanded (2 K/V groups instead of 32 expanded heads)
+    for layer in model.transformer.encoder.layers:
+        if hasattr(layer.self_attention.core_attention, 'grouped_kv'):
+            layer.self_attention.core_attention.grouped_kv = True
+    ms_grouped, logits_grouped = timed(lambda: model(ids))
     le, lh = logits_exact.float(), logits_hyper.float()
     dev_rel = ((lh - le).norm() / le.norm()).item()
     top1 = bool((le.argmax(-1) == lh.argmax(-1)).all())
     print(json.dumps({'workload': f'ChatGLM2-6B-shaped decoder, random init, {a.layers} blocks, hidden {a.hidden}, prefill 1 x {a.seq_len}',
                       'patched_blocks': a.patch_layers, 'exact_prefill_ms': ms_exact, 'hyper_prefill_ms': ms_hyper,
                       'exact_tokens_per_s': a.seq_len / ms_exact * 1e3, 'hyper_tokens_per_s': a.seq_len / ms_hyper * 1e3,
-                      'speedup': ms_exact / ms_hyper, 'last_logits_rel_deviation': dev_rel, 'last_token_top1_same': top1}))
+                      'speedup': ms_exact / ms_hyper, 'last_logits_rel_deviation': dev_rel, 'last_token_top1_same': top1,
+                      'hyper_grouped_kv_prefill_ms': ms_grouped, 'speedup_grouped_kv': ms_exact / ms_grouped,
+                      'grouped_vs_expanded_logits_rel_deviation': ((logits_grouped.float() - lh).norm() / lh.norm()).item()}))
 
 
 if __name__ == '__main__':

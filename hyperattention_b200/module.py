@@ -130,6 +130,17 @@ class HyperAttention(torch.nn.Module):
         batch_size, n_heads, n_key, dim = key.shape
         scale = scale or dim ** (-0.5)
         assert n_query == n_key
+        if n_heads != query.shape[1]:
+            # Grouped-query attention: fewer K/V heads than query heads (not in the reference, which is handed K/V already
+            # expanded to every query head, chatglm_fast_attention.py:53-58).  The single-call paths hash and sort K once
+            # per K/V head and never expand; every other path expands here.
+            assert query.shape[1] % n_heads == 0 and value.shape[1] == n_heads, 'query heads must be a multiple of the K/V heads'
+            grouped_ok = self.sampling == 'reference' and n_key >= self.min_seq_len and all(
+                t.is_contiguous() for t in (query, key, value)) and \
+                ((causal and n_key > self.min_seq_len and self.fused_causal and self._regular_causal(n_key)) or (not causal and self.fused_calls and query.dtype == self.lsh.proj_dir.dtype))
+            if not grouped_ok:
+                rep = query.shape[1] // n_heads
+                key, value = key.repeat_interleave(rep, dim=1), value.repeat_interleave(rep, dim=1)
 
         if causal is False:
             attn, lse = self.forward_no_causal_mask(query, key, value, scale)

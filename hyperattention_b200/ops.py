@@ -472,6 +472,7 @@ class CausalHyperFunc(torch.autograd.Function):
         p.levels, p.block_size, p.sample_size, p.lsh_bits = levels, block_size, sample_size, proj_f32.shape[1]
         p.keep_parts = 1 if (grad_reference and need_grad) else 0
         p.min_seq_len = min_seq_len
+        p.kv_group = H // k.shape[1]
         p.scale = scale
         p.q, p.k, p.v, p.proj, p.o, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(proj_f32), _ptr(o), _ptr(lse)
         _set_status(p, dev)
@@ -504,6 +505,7 @@ class CausalHyperFunc(torch.autograd.Function):
         p.B, p.H, p.n, p.d, p.dv = B, H, n, d, dv
         p.levels, p.block_size, p.sample_size, p.lsh_bits = levels, block_size, sample_size, proj_f32.shape[1]
         p.keep_parts, p.scale, p.min_seq_len = keep_parts, scale, min_seq_len
+        p.kv_group = H // k.shape[1]
         p.q, p.k, p.v, p.proj, p.o, p.lse = _ptr(q), _ptr(k), _ptr(v), _ptr(proj_f32), _ptr(o), _ptr(lse)
         p.saved, p.saved_bytes = _ptr(saved), saved.numel()
         _set_status(p, dev)
@@ -531,6 +533,7 @@ class NonCausalHyperFunc(torch.autograd.Function):
         p.dtype, p.flags = _dtype_id(q), flags
         p.B, p.H, p.n, p.d, p.dv = B, H, n, d, v.shape[-1]
         p.block_size, p.sample_size, p.lsh_bits, p.scale = block_size, sample_size, proj_f32.shape[1], scale
+        p.kv_group = H // k.shape[1]
         p.q, p.k, p.v, p.proj = _ptr(q), _ptr(k), _ptr(v), _ptr(proj_f32)
         _set_status(p, q.device)
         return p
@@ -541,7 +544,8 @@ class NonCausalHyperFunc(torch.autograd.Function):
         assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
         assert q.dtype == k.dtype == v.dtype, 'All tensors must have the same type'
         B, H, n, d = q.shape
-        assert k.shape == (B, H, n, d), 'query and key sequence lengths must be equal'
+        assert k.shape[0] == B and k.shape[2:] == (n, d), 'query and key sequence lengths must be equal'
+        assert H % k.shape[1] == 0 and v.shape[:3] == k.shape[:3], 'query heads must be a multiple of the key/value heads'
         assert n % 128 == 0, 'keys sequence length must be divisible by 128'
         assert sample_size % 128 == 0
         dev = q.device
@@ -572,9 +576,9 @@ class NonCausalHyperFunc(torch.autograd.Function):
         do = do.contiguous()
         dev = q.device
         # one buffer for the three gradients (dq | dk | dv): one allocation per step
-        nq, nv = q.numel(), v.numel()
-        out = torch.empty(2 * nq + nv, dtype=q.dtype, device=dev)
-        dq, dk, dvv = out[:nq].view_as(q), out[nq:2 * nq].view_as(k), out[2 * nq:].view_as(v)
+        nq, nk, nv = q.numel(), k.numel(), v.numel()
+        out = torch.empty(nq + nk + nv, dtype=q.dtype, device=dev)
+        dq, dk, dvv = out[:nq].view_as(q), out[nq:nq + nk].view_as(k), out[nq + nk:].view_as(v)
         p = NonCausalHyperFunc._params(q, k, v, proj_f32, block_size, sample_size, scale, flags)
         p.o, p.lse = _ptr(o), _ptr(lse)
         p.saved, p.saved_bytes = _ptr(saved), saved.numel()

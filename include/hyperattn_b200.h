@@ -130,6 +130,11 @@ typedef struct {
   int32_t d, dv;
   int32_t segs_per_head, span, q_off, k_off, m_q, m_k;
   int32_t block_size, sample_size; /* HA_MODE_HYPER */
+  int32_t kv_group;                /* grouped-query attention: this many consecutive query heads share one K/V head (0 or 1:
+                                      none).  k, v, k_idx, sample_idx and the dK/dV accumulators then have H / kv_group heads
+                                      (K is hashed and sorted once per group, never expanded -- the reference can only be
+                                      given expanded heads, chatglm_fast_attention.py:53-58); the backward sums a group's
+                                      contributions in the fp32 accumulators (no direct dK/dV outputs) */
   float scale;
   const void *q, *k, *v;
   int64_t q_sb, q_sh, q_sn, k_sb, k_sh, k_sn, v_sb, v_sh, v_sn;
@@ -214,6 +219,7 @@ typedef struct {
   int32_t B, H, n, d, dv;
   int32_t levels, block_size, sample_size, lsh_bits, keep_parts;
   int32_t min_seq_len;
+  int32_t kv_group;                /* as in ha_attn_params: k, v (and dk, dv_out) are [B, H / kv_group, n, *] */
   float scale;
   const void *q, *k, *v;           /* [B,H,n,*] contiguous */
   const float* proj;               /* [d][lsh_bits] */

@@ -32,8 +32,8 @@ def test_every_declared_symbol_is_exported(lib):
 def test_struct_layout_matches_header(lib):
     """sizes computed from the header's field lists with natural alignment"""
     from hyperattention_b200 import _lib
-    assert C.sizeof(_lib.AttnParams) == 17 * 4 + 4 + 3 * 8 + 9 * 8 + 3 * 8 + 8 + 3 * 8 + 3 * 8 + 8 + 3 * 8 + 4 * 8 + 2 * 8 + 2 * 8 + 5 * 8
-    assert C.sizeof(_lib.CausalParams) == 13 * 4 + 4 + 6 * 8 + 4 * 8 + 6 * 8
+    assert C.sizeof(_lib.AttnParams) == 18 * 4 + 3 * 8 + 9 * 8 + 3 * 8 + 8 + 3 * 8 + 3 * 8 + 8 + 3 * 8 + 4 * 8 + 2 * 8 + 2 * 8 + 5 * 8
+    assert C.sizeof(_lib.CausalParams) == 15 * 4 + 4 + 6 * 8 + 4 * 8 + 6 * 8
 
 
 def test_argument_validation_without_a_gpu(lib):

@@ -222,3 +222,38 @@ def test_single_call_noncausal_path_matches_per_operator_path(dtype, smooth):
     assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
     for a, b in zip(outs[0][2:], outs[1][2:]):
         assert rel(a, b) < 1e-3
+
+
+@pytest.mark.parametrize('causal', [False, True])
+@pytest.mark.parametrize('dtype,d', [(torch.bfloat16, 128), (torch.bfloat16, 64), (torch.float32, 64)])
+def test_grouped_query_heads_match_expanded_heads(causal, dtype, d):
+    """Grouped-query attention: K/V with 2 heads serving 8 (bf16: 16) query heads, hashed and sorted once per K/V head,
+    against the same call with K/V expanded to every query head (what the reference is given,
+    chatglm_fast_attention.py:53-58): identical forward; dK/dV of a K/V head equal the sum over its group's expanded
+    heads; and one head group against the oracle."""
+    import hyperattention_b200 as ha
+    torch.manual_seed(65)
+    B, Hkv, rep, n = 1, 2, (8 if dtype == torch.bfloat16 else 4), 4096
+    H = Hkv * rep
+    q = torch.randn(B, H, n, d, device='cuda').to(dtype)
+    k, v = [torch.randn(B, Hkv, n, d, device='cuda').to(dtype) for _ in range(2)]
+    do = torch.randn(B, H, n, d, device='cuda').to(dtype)
+    mod = ha.HyperAttention(input_dim=d, min_seq_len=1024, rng=torch.Generator().manual_seed(7)).to(device='cuda', dtype=dtype)
+    qg, kg, vg = [t.clone().requires_grad_() for t in (q, k, v)]
+    o, lse = mod(qg, kg, vg, causal=causal, return_lse=True)
+    o.backward(do)
+    ke, ve = [t.repeat_interleave(rep, dim=1).clone().requires_grad_() for t in (k, v)]
+    qe = q.clone().requires_grad_()
+    oe, lse_e = mod(qe, ke, ve, causal=causal, return_lse=True)
+    oe.backward(do)
+    assert o.shape == (B, H, n, d) and kg.grad.shape == k.shape
+    assert torch.equal(o, oe) and torch.equal(lse, lse_e)
+    tol = 2e-4 if dtype == torch.float32 else 1e-2
+    assert rel(qg.grad, qe.grad) < tol
+    assert rel(kg.grad, ke.grad.float().view(B, Hkv, rep, n, d).sum(2)) < tol
+    assert rel(vg.grad, ve.grad.float().view(B, Hkv, rep, n, d).sum(2)) < tol
+    # the first K/V head and one of its query heads against the oracle
+    orc = O.HyperAttentionOracle(mod.lsh.proj_dir.float().cpu(), 256, 256, 1024, False)
+    ow, lw = orc(q[:, 1:2].float().cpu(), k[:, 0:1].float().cpu(), v[:, 0:1].float().cpu(), causal=causal, return_lse=True)
+    to = 1e-4 if dtype == torch.float32 else 2e-2
+    assert rel(o[:, 1:2], ow) < to and rel(lse[:, 1:2], lw) < to
