@@ -1,8 +1,10 @@
 """Builds libhyperattn_b200.so for sm_100a with nvcc, in-tree (next to the Python package).
 
-    python hyperattention_b200/csrc/build.py [--force] [--verbose]
+    python hyperattention_b200/csrc/build.py [--force] [--verbose] [--timing]
 
-Object files are cached under csrc/build/ and rebuilt when a source or header is newer.
+Object files are cached under csrc/build/ and rebuilt when a source or header is newer.  --timing builds a second
+library, libhyperattn_b200_timing.so, with the kernels' per-phase cycle counters compiled in (-DHA_PHASE_TIMING; read by
+``python -m hyperattention_b200.phase_timing``); the product library never carries them.
 """
 import argparse
 import os
@@ -26,9 +28,11 @@ def _newer(path, deps):
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, timing=False):
     nvcc = os.environ.get('NVCC', 'nvcc')
-    bdir = os.path.join(HERE, 'build')
+    bdir = os.path.join(HERE, 'build', 'timing') if timing else os.path.join(HERE, 'build')
+    lib = os.path.join(PKG, 'libhyperattn_b200_timing.so') if timing else LIB
+    flags = NVCC_FLAGS + (['-DHA_PHASE_TIMING'] if timing else [])
     os.makedirs(bdir, exist_ok=True)
     headers = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith('.cuh')]
     headers.append(os.path.join(ROOT, 'include', 'hyperattn_b200.h'))
@@ -42,7 +46,7 @@ def build(force=False, verbose=False):
         o = os.path.join(bdir, src[:-3] + '.o')
         objs.append(o)
         if force or _newer(o, [s] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (['-Xptxas', '-v'] if verbose else []) + ['-c', s, '-o', o]
+            cmd = [nvcc] + flags + (['-Xptxas', '-v'] if verbose else []) + ['-c', s, '-o', o]
             jobs.append(cmd)
 
     def run(cmd):
@@ -55,18 +59,19 @@ def build(force=False, verbose=False):
                 sys.stderr.write(' '.join(cmd) + '\n' + r.stdout + r.stderr)
             if r.returncode != 0:
                 raise RuntimeError('nvcc failed for ' + cmd[-3])
-    if force or jobs or _newer(LIB, objs):
-        cmd = [nvcc, '-shared', '-o', LIB] + objs
+    if force or jobs or _newer(lib, objs):
+        cmd = [nvcc, '-shared', '-o', lib] + objs
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError('link failed')
-    return LIB
+    return lib
 
 
 if __name__ == '__main__':
     ap = argparse.ArgumentParser()
     ap.add_argument('--force', action='store_true')
     ap.add_argument('--verbose', action='store_true')
+    ap.add_argument('--timing', action='store_true')
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.timing))
