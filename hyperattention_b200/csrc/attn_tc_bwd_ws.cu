@@ -19,8 +19,9 @@
 //     is in its tensor phases meanwhile.
 //   * drain group (128 threads, thread = TMEM lane): dK / dV rows of a finished key tile, dQ rows of a finished query
 //     tile -> global memory (typed rows, or fp32 reductions into accumulators / slot buffers).
-//   * loader warp: gathers rows by index with cp.async into two K/V stages and two (Q, dO, lse, delta) stages; the
-//     copies signal the "full" barriers themselves, the warp only waits for free buffers and runs ahead.
+//   * three loader warps, one per operand stream (K tiles: ring of three; V tiles: ring of two; (Q, dO, lse, delta): one
+//     stage per query tile of the item): rows gathered by index with cp.async; the copies signal the "full" barriers
+//     themselves, a loader only waits for free buffers and runs ahead.  The rows of the next tile are pulled into L2 first.
 //   * five MMA-issuing threads (one per warp), one product each: S^T, dP^T, dV, dK of every half, dQ of every pair.
 //     One thread gets a tcgen05.mma accepted only about every 100 cycles, whatever its shape, while the tensor pipe
 //     finishes an M 128 x N 64 x K 16 step in under 60 (measured); five issuers keep the pipe fed and keep the 4-instruction
