@@ -7,7 +7,8 @@ Run once, in a container that has the reference checkout (path given by --refere
 Two families of vectors are written (float16/float32 as noted, all tiny):
 
 * ``kernel_*.pt``: the reference's own Triton kernels (``_angular_lsh_kernel``, ``_fwd_hyper_kernel``,
-  the three hyper backward kernels, the flash forward kernel) executed by the Triton interpreter on CPU
+  the three hyper backward kernels -- also at sample_size 256 and head dim 128 --, the flash forward and backward
+  kernels) executed by the Triton interpreter on CPU
   tensors in float16.  The host launchers assert CUDA, so the ``@triton.jit`` objects are launched
   directly with the launchers' own argument lists.
 * ``module_*.pt``: the reference's own ``HyperAttention.forward`` (recursion, views, merge, cat, autograd)
@@ -115,6 +116,7 @@ def kernel_hyper(ref, out_dir):
         'smooth':  (1, 2, 512, 64, 64, 256, 128, True, True),
         'nosamp':  (1, 1, 384, 64, 64, 256, 0, False, True),
         'd128':    (1, 1, 256, 128, 64, 128, 128, False, False),
+        'd128bwd': (1, 1, 256, 128, 128, 128, 128, False, True),
     }
     for tag, (B, H, n, d, dv, bsz, ssz, smooth, with_bwd) in cases.items():
         q = torch.randn(B, H, n, d).to(torch.float16)
@@ -134,6 +136,74 @@ def kernel_hyper(ref, out_dir):
             rec.update({'do': do, 'dq': T(dq).contiguous(), 'dk': T(dk).contiguous(), 'dv': T(dvv).contiguous()})
         torch.save(rec, os.path.join(out_dir, f'kernel_hyper_{tag}.pt'))
         print('hyper', tag, 'done')
+
+
+def kernel_hyper_s256_backward(ref, out_dir):
+    """The three backward kernels at sample_size = 256, the value every benchmark configuration uses.  The reference's
+    FORWARD at that size reads rows 128*d .. for its second sampled tile (src/hyper_attn_triton.py:144-145) while its
+    backward uses rows 0..255 (:576); so the backward kernels are given (o, lse) of the forward with rows 0..255 -- the
+    oracle's -- and what is pinned is their own arithmetic at two sampled tiles."""
+    from src import hyper_attn_triton as H_
+    from oracle import hyper_oracle as O
+    torch.manual_seed(13)
+    B, H, n, d, bsz, ssz = 1, 2, 512, 64, 256, 256
+    q = torch.randn(B, H, n, d).to(torch.float16)
+    k = torch.randn(B, H, n, d).to(torch.float16)
+    k[:, :, :ssz] *= 1.5
+    v = torch.randn(B, H, n, d).to(torch.float16)
+    do = torch.randn(B, H, n, d).to(torch.float16)
+    qi = torch.sort(torch.randint(0, 16, (B, H, n)), dim=2, stable=True)[1]
+    ki = torch.sort(torch.randint(0, 16, (B, H, n)), dim=2, stable=True)[1]
+    scale = 1.0 / math.sqrt(d)
+    T = lambda t: t.transpose(1, 2)
+    o, lse = O.hyper_attn_func(T(q), T(k), T(v), T(qi), T(ki), bsz, ssz, scale, False)
+    o = o.contiguous()
+    dq, dk, dvv = _launch_hyper_bwd(H_, T(do), T(q), T(k), T(v), T(qi), T(ki), o, lse.contiguous(), bsz, ssz, scale, False)
+    torch.save({'q': q, 'k': k, 'v': v, 'q_sort_idx': qi, 'k_sort_idx': ki, 'block_size': bsz, 'sample_size': ssz, 'smooth_block': False,
+                'scale': scale, 'o': T(o).contiguous(), 'lse': lse, 'do': do, 'dq': T(dq).contiguous(), 'dk': T(dk).contiguous(),
+                'dv': T(dvv).contiguous()}, os.path.join(out_dir, 'kernel_hyper_s256bwd.pt'))
+    print('hyper s256bwd done')
+
+
+def kernel_flash_backward(ref, out_dir):
+    """_bwd_preprocess_do_o_dot and _bwd_kernel of the exact attention (src/flash_attn_triton.py:271-312, :651-792) under
+    the interpreter, launched as _flash_attn_backward does (:830-990), on the forward kernel's own (o, lse)."""
+    from src import flash_attn_triton as F_
+    torch.manual_seed(14)
+    jit = F_._bwd_kernel
+    while not hasattr(jit, 'run') or hasattr(jit, 'fn') and not type(jit).__name__.startswith(('JIT', 'Interpreted')):
+        jit = jit.fn
+    for tag, (B, H, n, d, causal) in {'causal': (1, 2, 256, 64, True), 'full': (1, 1, 256, 64, False)}.items():
+        q = torch.randn(B, n, H, d).to(torch.float16)
+        k = torch.randn(B, n, H, d).to(torch.float16)
+        v = torch.randn(B, n, H, d).to(torch.float16)
+        do = torch.randn(B, n, H, d).to(torch.float16)
+        n_r = math.ceil(n / 128) * 128
+        lse = torch.empty(B, H, n_r, dtype=torch.float32)
+        o = torch.empty_like(q)
+        scale = 1.0 / math.sqrt(d)
+        BH = max(1 << (d - 1).bit_length(), 16)
+        F_._fwd_kernel.fn[(math.ceil(n / 128), B * H)](
+            q, k, v, None, o, lse, scale, q.stride(0), q.stride(2), q.stride(1), k.stride(0), k.stride(2), k.stride(1),
+            v.stride(0), v.stride(2), v.stride(1), 0, 0, 0, o.stride(0), o.stride(2), o.stride(1), H, n, n, n_r, d,
+            n // 32, n // 32, 'none', causal, BH,
+            EVEN_M=n % 128 == 0, EVEN_N=n % 128 == 0, EVEN_HEADDIM=True, BLOCK_M=128, BLOCK_N=128)
+        delta = torch.empty_like(lse)
+        F_._bwd_preprocess_do_o_dot[(math.ceil(n / 128), B * H)](
+            o, do, delta, o.stride(0), o.stride(2), o.stride(1), do.stride(0), do.stride(2), do.stride(1), H, n, n_r, d,
+            BLOCK_M=128, BLOCK_HEADDIM=BH)
+        dq_accum = torch.zeros(B, n, H, d, dtype=torch.float32)
+        dk, dvv = torch.empty_like(k), torch.empty_like(v)
+        jit[(1, B * H)](
+            q, k, v, None, do, dq_accum, dk, dvv, lse, delta, scale,
+            q.stride(0), q.stride(2), q.stride(1), k.stride(0), k.stride(2), k.stride(1), v.stride(0), v.stride(2), v.stride(1),
+            0, 0, 0, do.stride(0), do.stride(2), do.stride(1), dq_accum.stride(0), dq_accum.stride(2), dq_accum.stride(1),
+            dk.stride(0), dk.stride(2), dk.stride(1), dvv.stride(0), dvv.stride(2), dvv.stride(1), H, n, n, n_r, d, n // 32, n // 32,
+            'none', causal, BH, SEQUENCE_PARALLEL=False, EVEN_M=n % 128 == 0, EVEN_N=n % 128 == 0, EVEN_HEADDIM=True,
+            BLOCK_M=128, BLOCK_N=128)
+        torch.save({'q': q, 'k': k, 'v': v, 'do': do, 'causal': causal, 'scale': scale, 'o': o, 'lse': lse[:, :, :n].clone(),
+                    'dq': dq_accum.to(q.dtype), 'dk': dk, 'dv': dvv}, os.path.join(out_dir, f'kernel_flash_bwd_{tag}.pt'))
+        print('flash backward', tag, 'done')
 
 
 def kernel_flash(ref, out_dir):
@@ -214,7 +284,8 @@ def main():
     ap.add_argument('--only', default='')
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
-    for name, fn in (('lsh', kernel_lsh), ('hyper', kernel_hyper), ('flash', kernel_flash), ('module', module_cases)):
+    for name, fn in (('lsh', kernel_lsh), ('hyper', kernel_hyper), ('hyper_s256bwd', kernel_hyper_s256_backward), ('flash', kernel_flash),
+                     ('flash_bwd', kernel_flash_backward), ('module', module_cases)):
         if args.only and name not in args.only.split(','):
             continue
         fn(args.reference, HERE)

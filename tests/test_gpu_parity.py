@@ -316,7 +316,7 @@ def test_direct_dk_dv_matches_fp32_accumulators(ha, cfg):
         assert g.dtype == dtype and rel(g, w) < 6e-3
 
 
-@pytest.mark.parametrize('tag', ['plain', 'smooth', 'nosamp', 'd128'])
+@pytest.mark.parametrize('tag', ['plain', 'smooth', 'nosamp', 'd128', 'd128bwd', 's256bwd'])
 def test_hyper_attn_golden_reference_kernels(ha, golden_dir, tag):
     """outputs of the reference's Triton kernels (fp16, interpreter) on their own inputs"""
     from hyperattention_b200 import _lib as L
@@ -373,6 +373,18 @@ def test_flash_fewer_keys_than_queries(ha):
     o, lse = ha.flash_attn_func(dev(q), dev(k), dev(v))
     ow, lw = O.flash_attn_func(q, k, v)
     assert rel(o, ow) < 1e-4 and rel(lse, lw) < 1e-4
+
+
+@pytest.mark.parametrize('tag', ['causal', 'full'])
+def test_flash_backward_golden_reference_kernels(ha, golden_dir, tag):
+    """forward and backward of the reference's exact-attention Triton kernels (fp16, interpreter) on their own inputs"""
+    r = torch.load(os.path.join(golden_dir, f'kernel_flash_bwd_{tag}.pt'))
+    n = r['q'].shape[1]
+    q, k, v = [dev(r[x]).requires_grad_() for x in 'qkv']
+    o, lse = ha.flash_attn_func(q, k, v, None, r['causal'], r['scale'])
+    assert rel(o, r['o']) < 2e-3 and rel(lse[:, :, :n], r['lse']) < 1e-3
+    o.backward(dev(r['do']))
+    assert rel(q.grad, r['dq']) < 5e-3 and rel(k.grad, r['dk']) < 5e-3 and rel(v.grad, r['dv']) < 5e-3
 
 
 @pytest.mark.parametrize('tag', ['causal', 'full'])

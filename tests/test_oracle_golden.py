@@ -30,10 +30,12 @@ def test_lsh_matches_reference_kernel_and_hash_torch(golden_dir, tag):
     assert torch.equal(O.gray_table(r['proj_dir'].shape[-1]), r['perm'])
 
 
-@pytest.mark.parametrize('tag', ['plain', 'smooth', 'nosamp', 'd128'])
+@pytest.mark.parametrize('tag', ['plain', 'smooth', 'nosamp', 'd128', 'd128bwd', 's256bwd'])
 def test_hyper_attn_matches_reference_kernels(golden_dir, tag):
     """fp16 Triton-interpreter output of _fwd_hyper_kernel and the three backward kernels; tolerance is fp16
-    rounding of inputs/outputs (1e-3 relative in norm)."""
+    rounding of inputs/outputs (1e-3 relative in norm).  's256bwd': sample_size = 256, where only the reference's backward
+    is usable (its forward reads other rows there); the fixture's (o, lse) are those of rows 0..255, which is what the
+    backward kernels were given."""
     r = _load(golden_dir, f'kernel_hyper_{tag}.pt')
     q, k, v = [r[x].float().requires_grad_() for x in 'qkv']
     o, lse = O.hyper_attn_func(T(q), T(k), T(v), T(r['q_sort_idx']), T(r['k_sort_idx']), r['block_size'],
@@ -56,6 +58,18 @@ def test_smooth_block_reference_backward_is_not_the_forward_gradient(golden_dir)
                              r['sample_size'], r['scale'], True, None, True)
     T(o).backward(r['do'].float())
     assert rel(k.grad, r['dk']) > 0.1
+
+
+@pytest.mark.parametrize('tag', ['causal', 'full'])
+def test_flash_backward_matches_reference_kernels(golden_dir, tag):
+    """_bwd_preprocess_do_o_dot + _bwd_kernel of the exact attention under the interpreter (fp16)"""
+    r = _load(golden_dir, f'kernel_flash_bwd_{tag}.pt')
+    n = r['q'].shape[1]
+    q, k, v = [r[x].float().requires_grad_() for x in 'qkv']
+    o, lse = O.flash_attn_func(q, k, v, None, r['causal'], r['scale'])
+    assert rel(o, r['o']) < 1e-3 and rel(lse[:, :, :n], r['lse']) < 1e-5
+    o.backward(r['do'].float())
+    assert rel(q.grad, r['dq']) < 2e-3 and rel(k.grad, r['dk']) < 2e-3 and rel(v.grad, r['dv']) < 2e-3
 
 
 @pytest.mark.parametrize('tag', ['causal', 'full'])
