@@ -83,6 +83,37 @@ __global__ void bwd_finish_kernel(const ha_attn_params p, long long total) {
   *reinterpret_cast<uint4*>(out) = raw;
 }
 
+// HA_FLAG_CHECK_INDICES: every entry of an index array must be a row of its segment.
+__global__ void index_check_kernel(const int32_t* __restrict__ idx, long long count, int limit, int32_t* status, int32_t* status_host) {
+  bool bad = false;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+    const int v = idx[i];
+    bad |= v < 0 || v >= limit;
+  }
+  if (__syncthreads_or(bad) && threadIdx.x == 0) {
+    if (status) atomicExch(status, HA_DEV_BAD_INDEX);
+    if (status_host) {
+      *reinterpret_cast<volatile int32_t*>(status_host) = HA_DEV_BAD_INDEX;
+      __threadfence_system();
+    }
+  }
+}
+
+static int check_indices(const ha_attn_params& p, cudaStream_t st) {
+  if (!p.status) return HA_ERR_INVALID;
+  const long long segs = (long long)p.B * p.H * p.segs_per_head;
+  const long long ksegs = p.kv_group > 1 ? segs / p.kv_group : segs;
+  struct { const int32_t* ptr; long long count; int limit; } arr[3] = {
+      {p.q_idx, segs * p.m_q, p.m_q}, {p.k_idx, ksegs * p.m_k, p.m_k}, {p.sample_idx, ksegs * p.sample_size, p.m_k}};
+  for (auto& a : arr) {
+    if (!a.ptr || a.count == 0) continue;
+    const long long want = (a.count + 255) / 256;
+    index_check_kernel<<<(unsigned)(want < 148 * 8 ? want : 148 * 8), 256, 0, st>>>(a.ptr, a.count, a.limit, p.status, p.status_host);
+    HA_LAUNCHED("ha_attn index check");
+  }
+  return HA_OK;
+}
+
 // One warp, one mbarrier that nobody arrives at: the wait runs out after `polls` polls and is reported like any other.
 __global__ void wait_probe_kernel(int32_t* status, int32_t* status_host, int polls) {
   __shared__ uint64_t bar_mem;
@@ -112,6 +143,7 @@ int ha_attn_fwd(const ha_attn_params* p, void* stream) {
   int rc = check_common(*p, false);
   if (rc != HA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  if ((p->flags & HA_FLAG_CHECK_INDICES) && p->mode == HA_MODE_HYPER && (rc = check_indices(*p, st)) != HA_OK) return rc;
   if (!(p->flags & HA_FLAG_FORCE_SIMT) && ws_fwd_supported(*p)) return ws_attn_fwd(*p, st);
   if (!(p->flags & HA_FLAG_FORCE_SIMT) && tc_supported(*p)) return tc_attn_fwd(*p, st);
   return simt_attn_fwd(*p, st);
@@ -122,6 +154,7 @@ int ha_attn_bwd(const ha_attn_params* p, void* stream) {
   int rc = check_common(*p, true);
   if (rc != HA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  if ((p->flags & HA_FLAG_CHECK_INDICES) && p->mode == HA_MODE_HYPER && (rc = check_indices(*p, st)) != HA_OK) return rc;
   if (p->flags & HA_FLAG_BWD_KV_INIT) {
     // one work item must own a key tile's whole dK/dV: exact attention with a single chunk of query tiles
     if (p->mode != HA_MODE_FLASH || p->m_q > 16 * TILE || p->dk_out) return HA_ERR_INVALID;

@@ -54,6 +54,8 @@ __device__ __forceinline__ bool slot_dropped(const ha_attn_params& p, int seg, i
 
 template <typename T>
 __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_fwd_kernel(const ha_attn_params p, long long total_queries) {
+  __shared__ int s_bail;
+  if (cta_sees_failure(p.status, &s_bail)) return;   // a failed index check or an earlier timeout: touch nothing
   __shared__ float sq[SIMT_WARPS][MAXD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long wq = (long long)blockIdx.x * SIMT_WARPS + warp;
@@ -192,6 +194,8 @@ __device__ __forceinline__ int qlist_row(const ha_attn_params& p, int seg, const
 template <typename T>
 __global__ void __launch_bounds__(SIMT_WARPS * 32) attn_simt_bwd_kernel(const ha_attn_params p, int phase, int n_keys_per_seg,
                                                                         int chunks_per_key, long long total_items) {
+  __shared__ int s_bail;
+  if (cta_sees_failure(p.status, &s_bail)) return;   // a failed index check or an earlier timeout: touch nothing
   __shared__ float sk[SIMT_WARPS][MAXD];
   __shared__ float sv[SIMT_WARPS][MAXD];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

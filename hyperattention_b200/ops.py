@@ -55,12 +55,17 @@ def _set_status(p, device):
     p.status, p.status_host = _ptr(dev_w), C.c_void_p(host_w.data_ptr())
 
 
+def _status_text(v):
+    return {L.DEV_TIMEOUT: 'a device-side wait timed out',
+            L.DEV_BAD_INDEX: 'an index array holds a row outside its segment (index check)'}.get(v, 'the device reported a failure')
+
+
 def _raise_if_failed(dev_w, host_w):
     v = int(host_w[0])
     if v != 0:
         host_w.zero_()
         dev_w.zero_()
-        raise RuntimeError(f'hyperattention_b200: a device-side wait timed out in an earlier launch (status {v}); '
+        raise RuntimeError(f'hyperattention_b200: {_status_text(v)} in an earlier launch (status {v}); '
                            'results produced since then are undefined')
 
 
@@ -72,7 +77,7 @@ def check_device_status(device=None, reset=True):
         if reset:
             dev_w.zero_()
             host_w.zero_()
-        raise RuntimeError(f'hyperattention_b200: device-side wait timed out (status {v})')
+        raise RuntimeError(f'hyperattention_b200: {_status_text(v)} (status {v})')
 
 
 def _cuda(*ts):

@@ -26,7 +26,8 @@ enum {
   HA_ERR_CUDA = -4,         /* a CUDA runtime call (launch, attribute) failed; see ha_last_cuda_error */
   HA_ERR_TOO_LARGE = -5,    /* beyond a size limit of the entry point: a grid dimension (segments, work items), or the
                                built-in scratch array of ha_seg_sort_noalloc */
-  HA_DEV_TIMEOUT = 1        /* a bounded device-side wait gave up (written to the caller's status word) */
+  HA_DEV_TIMEOUT = 1,       /* a bounded device-side wait gave up (written to the caller's status word) */
+  HA_DEV_BAD_INDEX = 2      /* HA_FLAG_CHECK_INDICES: q_idx / k_idx / sample_idx holds a row outside its segment */
 };
 
 enum { HA_BF16 = 0, HA_FP16 = 1, HA_FP32 = 2 };
@@ -47,6 +48,11 @@ enum {
   HA_FLAG_FORCE_SIMT = 32,   /* use the fp32 CUDA-core kernels even where a tensor-core kernel exists */
   HA_FLAG_NO_WS = 128,       /* keep the earlier kernels (forward: one tile per CTA; backward: one thread-block role) where the
                                 persistent warp-specialised ones apply */
+  HA_FLAG_CHECK_INDICES = 256,/* HA_MODE_HYPER, needs `status`: a checking kernel runs first and looks at every entry of q_idx, k_idx
+                                and sample_idx; an entry outside [0, rows of the segment) sets the status words to
+                                HA_DEV_BAD_INDEX, and the attention kernel that follows returns at once instead of reading
+                                (and faulting on) a row that does not exist.  The reference relies on its caller here
+                                (torch.sort cannot produce such an index; a hand-made permutation can). */
   HA_FLAG_BWD_KV_INIT = 64   /* backward, HA_MODE_FLASH with m_q <= 2048 on the tensor-core kernel: dk_acc / dv_acc hold
                                 garbage; the launch stores (not adds) every key row of every segment */
 };

@@ -257,3 +257,30 @@ def test_grouped_query_heads_match_expanded_heads(causal, dtype, d):
     ow, lw = orc(q[:, 1:2].float().cpu(), k[:, 0:1].float().cpu(), v[:, 0:1].float().cpu(), causal=causal, return_lse=True)
     to = 1e-4 if dtype == torch.float32 else 2e-2
     assert rel(o[:, 1:2], ow) < to and rel(lse[:, 1:2], lw) < to
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_index_check_turns_a_bad_permutation_into_a_status(dtype):
+    """HA_FLAG_CHECK_INDICES: a hand-made permutation with a row outside the sequence does not make the kernels read a row
+    that does not exist (the checking kernel sets the status word, the attention kernel returns at once); the next call
+    into the library raises.  With valid indices the flag changes nothing."""
+    import hyperattention_b200 as ha
+    from hyperattention_b200 import _lib as L
+    torch.manual_seed(66)
+    B, H, n, d = 1, 2, 1024, 64
+    q, k, v = [torch.randn(B, n, H, d, device='cuda').to(dtype) for _ in range(3)]
+    qi = torch.stack([torch.randperm(n) for _ in range(B * H)]).view(B, H, n).transpose(1, 2).cuda()
+    ki = torch.stack([torch.randperm(n) for _ in range(B * H)]).view(B, H, n).transpose(1, 2).cuda()
+    o0, l0 = ha.hyper_attn_func(q, k, v, qi, ki, 256, 256)
+    o1, l1 = ha.hyper_attn_func(q, k, v, qi, ki, 256, 256, None, False, None, L.FLAG_CHECK_INDICES)
+    assert torch.equal(o0, o1) and torch.equal(l0, l1)
+    ha.check_device_status()
+    bad = ki.clone()
+    bad[0, 17, 1] = n + 5                       # one key position of head 1 points past the sequence
+    ha.hyper_attn_func(q, k, v, qi, bad, 256, 256, None, False, None, L.FLAG_CHECK_INDICES)     # no fault, no exception yet
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match='index'):
+        ha.hyper_attn_func(q, k, v, qi, ki, 256, 256)
+    o2, _ = ha.hyper_attn_func(q, k, v, qi, ki, 256, 256)            # healthy again
+    assert torch.equal(o2, o0)
+    ha.check_device_status()
