@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   // ---- once per CTA: barrier, TMEM ----
   const uint32_t bar = smem_u32(&mma_bar);
   if (tid == 0) {
-    mbar_init(bar, 1);
+    mbar_init(bar, 5);      // one arrival per batch from each of the five MMA-issuing threads
     mbar_fence_init();
   }
   if (tid < 32) tmem_alloc(smem_u32(&tmem_slot), 512);
@@ -417,40 +417,59 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
   float delta_cur = qrow_cur >= 0 ? delta_base[qrow_cur] : 0.f;
   int qrow_next = cur.qrow1;
 
-  // S = Q K^T and dP = dO V^T of the query tile in stage `stg`
-  auto issue_mma1 = [&](int stg, bool second = false) {
+  // The MMAs of a batch are issued by five threads, one product each: one thread gets a tcgen05.mma accepted only about
+  // every 110-130 cycles whatever its shape (measured), so the 32 instructions of a batch from one thread cost twice what
+  // the tensor pipe needs for them.  Thread 0: dV, thread 32: dK, thread 64: dQ, thread 96: S, thread 160: dP.  Every one
+  // of them arrives on the batch's barrier exactly once: a commit after its instructions, or a plain arrival when the
+  // batch has none for it.
+  const int issuer = tid == 0 ? 0 : tid == 32 ? 1 : tid == 64 ? 2 : tid == 96 ? 3 : tid == 160 ? 4 : -1;
+  // S = Q K^T (issuer 3) and dP = dO V^T (issuer 4) of the query tile in stage `stg`; `on` = the batch has these products
+  auto issue_mma1 = [&](bool on, int stg, bool second = false) {
+    if (issuer != 3 && issuer != 4) return;
+    if (!on) { mbar_arrive(bar); return; }
     const uint32_t sQ = s_base + Cfg::OFF_Q + stg * Cfg::Q_BYTES, sDO = s_base + Cfg::OFF_DO + stg * Cfg::DO_BYTES;
     const uint32_t sK = s_base + (second ? Cfg::OFF_K2 : Cfg::OFF_K), sV = s_base + (second ? Cfg::OFF_V2 : Cfg::OFF_V);
+    if (issuer == 3) {
 #pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-      const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-      mma_ss(tS, smem_desc(sQ + off, 16, 1024), smem_desc(sK + off, 16, 1024), id_s, kk > 0);
-    }
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
+        mma_ss(tS, smem_desc(sQ + off, 16, 1024), smem_desc(sK + off, 16, 1024), id_s, kk > 0);
+      }
+    } else {
 #pragma unroll
-    for (int kk = 0; kk < DV / 16; ++kk) {
-      const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-      mma_ss(tDP, smem_desc(sDO + off, 16, 1024), smem_desc(sV + off, 16, 1024), id_s, kk > 0);
+      for (int kk = 0; kk < DV / 16; ++kk) {
+        const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
+        mma_ss(tDP, smem_desc(sDO + off, 16, 1024), smem_desc(sV + off, 16, 1024), id_s, kk > 0);
+      }
     }
+    mma_commit(bar);
   };
-  // dV += P^T dO, dK += dS^T Q, dQ = dS K for the query tile in stage `stg`
+  // dV += P^T dO (issuer 0), dK += dS^T Q (issuer 1), dQ = dS K (issuer 2) for the query tile in stage `stg`
   // acc0: dV / dK accumulate onto what TMEM holds; dq_acc: so does dQ (paired block item, second key tile)
-  auto issue_mma2 = [&](int stg, uint32_t acc0, uint32_t t_dq, bool second = false, uint32_t dq_acc = 0) {
+  auto issue_mma2 = [&](bool on, int stg, uint32_t acc0, uint32_t t_dq, bool second = false, uint32_t dq_acc = 0) {
+    if (issuer < 0 || issuer > 2) return;
+    if (!on) { mbar_arrive(bar); return; }
     const uint32_t sQ = s_base + Cfg::OFF_Q + stg * Cfg::Q_BYTES, sDO = s_base + Cfg::OFF_DO + stg * Cfg::DO_BYTES;
     const uint32_t sK = s_base + (second ? Cfg::OFF_K2 : Cfg::OFF_K);
+    if (issuer == 0) {
 #pragma unroll
-    for (int kk = 0; kk < TILE / 16; ++kk)
-      mma_ss(tDV, smem_desc(s_base + Cfg::OFF_P + kk * 2048, TILE * 128, 1024), smem_desc(sDO + kk * 2048, TILE * 128, 1024), id_dv,
-             acc0 | (kk > 0));
+      for (int kk = 0; kk < TILE / 16; ++kk)
+        mma_ss(tDV, smem_desc(s_base + Cfg::OFF_P + kk * 2048, TILE * 128, 1024), smem_desc(sDO + kk * 2048, TILE * 128, 1024), id_dv,
+               acc0 | (kk > 0));
+    } else if (issuer == 1) {
 #pragma unroll
-    for (int kk = 0; kk < TILE / 16; ++kk)
-      mma_ss(tDK, smem_desc(s_base + Cfg::OFF_DS + kk * 2048, TILE * 128, 1024), smem_desc(sQ + kk * 2048, TILE * 128, 1024), id_dk,
-             acc0 | (kk > 0));
+      for (int kk = 0; kk < TILE / 16; ++kk)
+        mma_ss(tDK, smem_desc(s_base + Cfg::OFF_DS + kk * 2048, TILE * 128, 1024), smem_desc(sQ + kk * 2048, TILE * 128, 1024), id_dk,
+               acc0 | (kk > 0));
+    } else {
 #pragma unroll
-    for (int kk = 0; kk < TILE / 16; ++kk) {
-      const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
-      mma_ss(t_dq, smem_desc(s_base + Cfg::OFF_DS + off, 16, 1024), smem_desc(sK + kk * 2048, TILE * 128, 1024), id_dq,
-             dq_acc | (kk > 0));
+      for (int kk = 0; kk < TILE / 16; ++kk) {
+        const uint32_t off = (kk >> 2) * (TILE * 128) + (kk & 3) * 32;
+        mma_ss(t_dq, smem_desc(s_base + Cfg::OFF_DS + off, 16, 1024), smem_desc(sK + kk * 2048, TILE * 128, 1024), id_dq,
+               dq_acc | (kk > 0));
+      }
     }
+    mma_commit(bar);
   };
   // P and dS of this thread's query row, its group's 64 key columns -> shared memory
   // weighted sampling (sampled items only): pair jj meets sorted query tile qt_first + jj; its log weight is added to
@@ -544,10 +563,10 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     uint8_t* sSTG = smem + Cfg::OFF_STG;
     // dQ rows of pair jp (TMEM buffer jp & 1) -> global: fp32 reduction into dq_acc, or -- a paired item whose TMEM
     // buffer holds the query tile's complete sum (final_dq) -- the final rows of dq_out
-    // under_batch: the drain runs while the batch issued just before executes.  The thread that issued it is held by the
-    // tensor pipe for about as long as the batch takes, so its warp's share of the drain would come after everybody
-    // else's and delay the next pair: the warp of the other group that sits on the same 32 TMEM lanes takes both
-    // column halves of those rows instead.
+    // under_batch: the drain runs while the batch issued just before executes.  A thread that issued eight of its
+    // instructions is held by the tensor pipe for about a thousand cycles, so the share of the drain of warp 0 (the dV
+    // issuer's) would come after everybody else's and delay the next pair: the warp of the other group that sits on the
+    // same 32 TMEM lanes takes both column halves of those rows instead.
     auto drain_dq = [&](int jp, int qrow_of_pair, bool under_batch) {
       if (final_dq && paired) {
         reduce_rows<D / 2, 2, T>(sSTG + wg * Cfg::STG_HALF, tDQ + (jp & 1) * D + lane_sel + wg * (D / 2), dq_base + wg * (D / 2), D,
@@ -570,10 +589,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (tid == 0) {
-      issue_mma1(0);
-      mma_commit(bar);
-    }
+    issue_mma2(false, 0, 0, tDQ);             // (first batch: S and dP of pair 0 only)
+    issue_mma1(true, 0);
     draw_next();                              // read after the pair loop's barriers, below
     int qrow_prev = -1;
     for (int jj = 0; jj < qt_count; ++jj) {
@@ -612,17 +629,14 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       tc_fence_before();
       __syncthreads();
       tc_fence_after();
-      if (tid == 0) {
-        if (paired) {
-          // dV / dK restart with each key tile; dQ of a query tile sums over both key tiles in its own TMEM buffer
-          // (key buffers alternate with the key tile jj / 2: A, B, and -- fused -- S0, S1)
-          issue_mma2(st, jj & 1, tDQ + (jj & 1) * D, (jj >> 1) & 1, jj >= 2 ? 1u : 0u);
-          if (jj + 1 < qt_count) issue_mma1(st ^ 1, ((jj + 1) >> 1) & 1);
-        } else {
-          issue_mma2(st, jj > 0, tDQ + (jj & 1) * D);
-          if (jj + 1 < qt_count) issue_mma1(st ^ 1);
-        }
-        mma_commit(bar);
+      if (paired) {
+        // dV / dK restart with each key tile; dQ of a query tile sums over both key tiles in its own TMEM buffer
+        // (key buffers alternate with the key tile jj / 2: A, B, and -- fused -- S0, S1)
+        issue_mma2(true, st, jj & 1, tDQ + (jj & 1) * D, (jj >> 1) & 1, jj >= 2 ? 1u : 0u);
+        issue_mma1(jj + 1 < qt_count, st ^ 1, ((jj + 1) >> 1) & 1);
+      } else {
+        issue_mma2(true, st, jj > 0, tDQ + (jj & 1) * D);
+        issue_mma1(jj + 1 < qt_count, st ^ 1);
       }
       HA_T_MARK(4)
       // underneath the batch: dQ of the previous pair (paired item: of query tile 0, complete after pair 2)
@@ -664,10 +678,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       __syncthreads();
       tc_fence_after();
       HA_T_MARK(1)
-      if (tid == 0) {
-        issue_mma1(0);
-        mma_commit(bar);
-      }
+      issue_mma2(false, 0, 0, tDQ);
+      issue_mma1(true, 0);
       if (jj == 0) draw_next();               // read after this loop (every iteration has barriers)
       if (!mbar_wait(bar, phase)) failed = true;
       phase ^= 1;
@@ -680,10 +692,8 @@ __global__ void __launch_bounds__(256) attn_tc_bwd_kernel(const ha_attn_params p
       __syncthreads();
       tc_fence_after();
       HA_T_MARK(3)
-      if (tid == 0) {
-        issue_mma2(0, jj > 0, tDQ);
-        mma_commit(bar);
-      }
+      issue_mma2(true, 0, jj > 0, tDQ);
+      issue_mma1(false, 0);
       if (!mbar_wait(bar, phase)) failed = true;
       phase ^= 1;
       tc_fence_after();

@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
 
   if (cta_sees_failure(p.status, &s_bail)) return;   // an earlier CTA gave up: drain quickly (uniform over the CTA)
   if (tid == 0) {
-    mbar_init(bar, 1);
+    mbar_init(bar, 2);      // one arrival from each of the two MMA-issuing threads per batch
     mbar_fence_init();
   }
   if (warp == 0) tmem_alloc(smem_u32(&tmem_slot), Cfg::TMEM_COLS);
@@ -244,7 +244,12 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (tid == 0) {
+  // Two threads issue the MMAs of a batch: thread 0 the P V product of key tile j, thread 32 S of key tile j + 1.  One thread
+  // gets a tcgen05.mma accepted only about every 110-130 cycles whatever its shape (measured), so the 12 instructions of a
+  // batch from one thread cost more than the tensor pipe needs for them; each thread arrives once per batch (a commit
+  // after its instructions, or a plain arrival when it has none).
+  if (tid == 0) mbar_arrive(bar);
+  if (tid == 32) {
     issue_s(0, tmem);
     mma_commit(bar);
   }
@@ -372,8 +377,15 @@ __global__ void __launch_bounds__(128) attn_tc_fwd_kernel(const ha_attn_params p
     tc_fence_after();
     if (tid == 0) {
       issue_pv(st, tP, tPV);
-      if (j + 1 < tl.n_tiles) issue_s(st ^ 1, tmem + (st ^ 1) * Cfg::REGION);
       mma_commit(bar);
+    }
+    if (tid == 32) {
+      if (j + 1 < tl.n_tiles) {
+        issue_s(st ^ 1, tmem + (st ^ 1) * Cfg::REGION);
+        mma_commit(bar);
+      } else {
+        mbar_arrive(bar);
+      }
     }
     HA_T_MARK(4)
     krow_cur = krow_next;
