@@ -86,12 +86,33 @@ class HyperAttention(torch.nn.Module):
         #              excluded, importance-weighted to stand for all keys outside the block (no reference counterpart).
         self.sampling = kwargs.get('sampling', 'reference')
         self.sample_generator = kwargs.get('sample_generator')   # torch.Generator on the inputs' device, or None
+        # Without a generator the draws come from a counter-based function of (sample_seed, number of the call, batch*head,
+        # slot) evaluated with integer ops on the device: reproducible, and computable bit for bit on the host.
+        self.sample_seed = int(kwargs.get('sample_seed', 0))
+        self.sample_calls = 0
         self.last_sample_idx = None
         assert self.grad_mode in ('reference', 'exact') and self.merge_mode in ('reference', 'exact')
         assert self.sampling in ('reference', 'uniform')
         self.lsh = AngularLSH(num_projs=self.lsh_num_projs, dim=(1, 1, input_dim), rng=kwargs.get('rng'))
 
     # ------------------------------------------------------------------------------------------
+    def _counter_u24(self, rows, S, device):
+        """24 uniform bits per (row, slot): top bits of the splitmix64 finaliser of (sample_seed, call number, row * S + slot),
+        in int64 arithmetic (wrap-around products; logical right shifts written as arithmetic shift + mask)."""
+        def c(v):                                   # a 64-bit constant as a signed Python int
+            return v - (1 << 64) if v >= (1 << 63) else v
+        def shr(x, k):
+            return (x >> k) & ((1 << (64 - k)) - 1)
+        def wrap(v):
+            v &= (1 << 64) - 1
+            return c(v)
+        base = wrap(self.sample_seed * 0x9E3779B97F4A7C15 + self.sample_calls * 0xD1B54A32D192ED03)
+        x = torch.arange(rows * S, device=device, dtype=torch.int64) + base
+        x = (x ^ shr(x, 30)) * c(0xBF58476D1CE4E5B9)
+        x = (x ^ shr(x, 27)) * c(0x94D049BB133111EB)
+        x = x ^ shr(x, 31)
+        return shr(x, 40).view(rows, S)
+
     def _flags(self):
         f = self.kernel_flags
         if self.smooth_block:
@@ -212,9 +233,13 @@ class HyperAttention(torch.nn.Module):
                 # sample_size equal strata of the key range (cheaper than a draw without replacement, lower variance)
                 n_k, S = key.shape[2], self.sample_size
                 edges = (torch.arange(S + 1, device=key.device, dtype=torch.int64) * n_k) // S
-                u = torch.rand(B * H, S, device=key.device, generator=self.sample_generator)
                 size = edges[1:] - edges[:-1]
-                sample_idx = (edges[:-1] + torch.minimum((u * size).long(), size - 1)).to(torch.int32)
+                if self.sample_generator is not None:
+                    u = torch.rand(B * H, S, device=key.device, generator=self.sample_generator)
+                    sample_idx = (edges[:-1] + torch.minimum((u * size).long(), size - 1)).to(torch.int32)
+                else:
+                    sample_idx = (edges[:-1] + ((size * self._counter_u24(B * H, S, key.device)) >> 24)).to(torch.int32)
+                    self.sample_calls += 1
                 self.last_sample_idx = sample_idx.view(B, H, self.sample_size)
                 weighted = True
             attn, lse = ops.hyper_attn_func(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2),

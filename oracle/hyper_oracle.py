@@ -107,6 +107,27 @@ def _default_sample_idx(sample_size: int, device=None) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 # Fused block-diagonal + sampled attention, one (batch, head) at a time
 # --------------------------------------------------------------------------------------------
+def uniform_sample_idx(seed: int, call: int, rows: int, sample_size: int, n: int) -> torch.Tensor:
+    """Sampled key rows of the uniform mode: int64 [rows, sample_size], row = batch * heads + head.
+
+    One draw from each of sample_size equal strata of [0, n): slot s of row r takes
+    start_s + ((size_s * u) >> 24) with u = the top 24 bits of mix64(seed, call, r * sample_size + s), where mix64 is the
+    splitmix64 finaliser.  Pure integer arithmetic in numpy uint64 -- a function of (seed, call, r, s) only, so the
+    module (which evaluates the same function with torch integer ops on the device) and this restatement agree bit for
+    bit.  No counterpart in the mounted reference (its sampled part reads rows 0..sample_size-1)."""
+    import numpy as np
+    with np.errstate(over='ignore'):
+        ctr = np.arange(rows * sample_size, dtype=np.uint64)
+        x = (np.uint64(seed) * np.uint64(0x9E3779B97F4A7C15) + np.uint64(call) * np.uint64(0xD1B54A32D192ED03) + ctr)
+        x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        x = x ^ (x >> np.uint64(31))
+    u24 = (x >> np.uint64(40)).astype(np.int64).reshape(rows, sample_size)
+    edges = (np.arange(sample_size + 1, dtype=np.int64) * n) // sample_size
+    start, size = edges[:-1], edges[1:] - edges[:-1]
+    return torch.from_numpy(start[None, :] + ((size[None, :] * u24) >> 24))
+
+
 def sample_tile_weights(n, ki, block_size, sample_idx, smooth):
     """Weighted sampling (no counterpart in the mounted reference; "parity unpinned"): for every sorted query tile t,
     which sampled slots are dropped because their key already lies in the tile's block window, and the log of the

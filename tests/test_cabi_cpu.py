@@ -139,3 +139,23 @@ def test_causal_level_arithmetic():
     assert not m._regular_causal(2048 * 3 + 2)     # leaves not 128-aligned
     m2 = ha.HyperAttention(min_seq_len=256, sample_size=512)
     assert not m2._regular_causal(4096)            # leaves too short for the sampled rows
+
+
+def test_counter_based_sample_indices_agree_with_the_oracle():
+    """The uniform sampling mode's draws are a function of (seed, call, batch*head, slot) in integer arithmetic: the
+    module's torch int64 version (run here on the CPU) and the oracle's numpy uint64 restatement agree bit for bit."""
+    import torch
+    import hyperattention_b200 as ha
+    from oracle import hyper_oracle as O
+    mod = ha.HyperAttention(input_dim=64, sample_size=256, sampling='uniform', sample_seed=2024)
+    for call, (rows, n) in enumerate([(6, 4096), (3, 1000), (32, 131072)]):
+        mod.sample_calls = call
+        S = mod.sample_size
+        u = mod._counter_u24(rows, S, 'cpu')
+        edges = (torch.arange(S + 1, dtype=torch.int64) * n) // S
+        size = edges[1:] - edges[:-1]
+        idx = edges[:-1] + ((size * u) >> 24)
+        want = O.uniform_sample_idx(2024, call, rows, S, n)
+        assert torch.equal(idx, want)
+        assert int(idx.min()) >= 0 and int(idx.max()) < n and bool((idx[:, 1:] > idx[:, :-1]).all())      # distinct, in range
+    assert 0.45 < float(u.float().mean()) / 2 ** 24 < 0.55

@@ -279,6 +279,16 @@ def test_module_uniform_sampling_mode(ha):
         assert rel(o1, T(ow)) < TOL[torch.bfloat16][0] and rel(lse1.squeeze(-1), lw) < TOL[torch.bfloat16][0]
     oc = mod(dev(q), dev(k), dev(v), causal=True)
     assert oc.shape == (B, H, n, d) and torch.isfinite(oc.float()).all()
+    # without a generator: counter-based draws, which the oracle computes on the host bit for bit (seed, call number)
+    mod2 = hb.HyperAttention(input_dim=d, block_size=128, sample_size=128, min_seq_len=256, sampling='uniform', sample_seed=11,
+                             rng=torch.Generator().manual_seed(1)).cuda().to(dtype=torch.bfloat16)
+    for call in range(2):
+        o3, lse3 = mod2(dev(q), dev(k), dev(v), return_lse=True)
+        want = O.uniform_sample_idx(11, call, B * H, 128, n).view(B, H, 128)
+        assert torch.equal(mod2.last_sample_idx.cpu().long(), want)
+        ow, lw = O.hyper_attn_func(T(q.float()), T(k.float()), T(v.float()), T(qi), T(ki), 128, 128, None, False, want, False, True)
+        if not (O.lsh_tie_mask(q, proj).any() or O.lsh_tie_mask(k, proj).any()):
+            assert rel(o3, T(ow)) < TOL[torch.bfloat16][0] and rel(lse3.squeeze(-1), lw) < TOL[torch.bfloat16][0]
 
 
 @pytest.mark.parametrize('cfg', [
