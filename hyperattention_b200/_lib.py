@@ -14,7 +14,7 @@ BF16, FP16, FP32 = 0, 1, 2
 MODE_HYPER, MODE_FLASH = 0, 1
 FLAG_CAUSAL, FLAG_SMOOTH, FLAG_MERGE, FLAG_MERGE_EXACT, FLAG_BWD_REF_SMOOTH, FLAG_FORCE_SIMT, FLAG_BWD_KV_INIT, FLAG_NO_WS = 1, 2, 4, 8, 16, 32, 64, 128
 FLAG_CHECK_INDICES = 256
-DEV_TIMEOUT, DEV_BAD_INDEX = 1, 2
+DEV_TIMEOUT, DEV_BAD_INDEX, DEV_BAD_LAUNCH = 1, 2, 3
 
 _STATUS = {-1: 'invalid argument (shape / stride / size not accepted)', -2: 'unsupported dtype',
            -3: 'workspace missing or too small', -4: 'CUDA runtime error', 1: 'device-side wait timed out',

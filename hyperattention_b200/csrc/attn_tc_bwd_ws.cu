@@ -46,7 +46,9 @@ constexpr int OFF_V = OFF_K + K_STAGES * TILE_B;               // V ring
 constexpr int OFF_QD = OFF_V + V_STAGES * TILE_B;              // stage y (query tile y of the item): Q, then dO
 constexpr int OFF_DS = OFF_QD + 2 * 2 * TILE_B;                // two buffers (pairs alternate) of two slabs (column halves)
 constexpr int OFF_LD = OFF_DS + 2 * 2 * TILE_B;                // per query-tile stage: lse[128], delta[128] (fp32)
-constexpr int SMEM = OFF_LD + 2 * 1024 + 1024;                 // + alignment slack
+constexpr int OFF_ST = OFF_LD + 2 * 1024;                      // staging tile of the drain group: 128 rows x 128 bytes
+constexpr int SMEM_USED = OFF_ST + TILE * 128;                 // from the 1024-byte aligned base
+constexpr int SMEM_LIMIT = 227 * 1024;                         // per CTA, static + dynamic
 constexpr int THREADS = 640;
 constexpr int COL_DV = 256, COL_DK = 320, COL_DQ = 384;
 // barrier slots (index + stage / buffer / query tile) and their arrivals per phase
@@ -64,11 +66,11 @@ enum {
   B_DS_FREE = 22,    // 2 x 1: dQ of the pair has read the dS buffer
   B_DQ_FULL = 24,    // 2 x 1: dQ of a query tile complete
   B_DQ_FREE = 26,    // 2 x 128: ... drained
-  B_LDT = 28,        // 2 x 256: lse / delta of a query tile pre-scaled by the elementwise threads
-  B_DS_FULL = 30,    // 2 x 512: both halves' dS slabs of a pair are in the buffer (every elementwise thread, twice)
-  B_ACC_FULL = 32,   // 2: dV and dK of a key tile complete
-  B_ACC_FREE = 33,   // 128: ... drained
-  N_BARS = 34
+  B_LDT = 28,        // (2 query tiles x 2 groups) x 128: an elementwise group has pre-scaled the lse / delta of its own columns
+  B_DS_FULL = 32,    // 2 x 512: both halves' dS slabs of a pair are in the buffer (every elementwise thread, twice)
+  B_ACC_FULL = 34,   // 2: dV and dK of a key tile complete
+  B_ACC_FREE = 35,   // 128: ... drained
+  N_BARS = 36
 };
 __device__ __forceinline__ int bar_count(int i) {
   if (i < B_K_EMPTY) return 32;
@@ -80,12 +82,39 @@ __device__ __forceinline__ int bar_count(int i) {
   if (i < B_P_READY) return 2;
   if (i < B_SF_S) return 256;
   if (i < B_DQ_FREE) return 1;          // stage-free (S, P), dS-free, dQ-full
-  if (i < B_LDT) return 128;
-  if (i < B_DS_FULL) return 256;
+  if (i < B_DS_FULL) return 128;        // dQ-free, pre-scaled lse / delta
   if (i < B_ACC_FULL) return 512;
   return i == B_ACC_FULL ? 2 : 128;
 }
 }  // namespace bws
+
+// Rotates the eight chunks (CW words each) of a row held in registers: afterwards chunk i is what chunk (i + rot) & 7 was.
+// Register arrays cannot be indexed by a run-time value: three conditional steps of 1, 2 and 4 chunks, selects only.
+template <int CW>
+__device__ __forceinline__ void bws_rot8(uint32_t (&w)[8 * CW], int rot) {
+#pragma unroll
+  for (int st = 1; st < 8; st <<= 1) {
+    const bool on = (rot & st) != 0;
+    uint32_t t[8 * CW];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int k = 0; k < CW; ++k) t[i * CW + k] = on ? w[((i + st) & 7) * CW + k] : w[i * CW + k];
+#pragma unroll
+    for (int i = 0; i < 8 * CW; ++i) w[i] = t[i];
+  }
+}
+// Bulk copies shared -> global of the copy engine (a thread's own row of the staging tile): plain store and fp32 add.
+__device__ __forceinline__ void bws_bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bws_bulk_add_f32(float* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bws_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// this thread's earlier bulk copies have read their source (the staging row may be rewritten) / have completed
+__device__ __forceinline__ void bws_bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bws_bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // 128 rows x 64 elements gathered by ONE warp: rows[q] = source row of tile row 32 q + lane (-1: zero fill)
 __device__ __forceinline__ void bws_gather_tile(uint32_t smem_base, const uint16_t* __restrict__ base, int64_t row_stride, const int (&rows)[4],
@@ -128,6 +157,22 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
   const bool dq_direct = p.dq_out != nullptr, kv_direct = p.dk_out != nullptr;
 
   if (cta_sees_failure(p.status, &s_bail)) return;   // an earlier CTA gave up: drain quickly (uniform over the CTA)
+  {
+    // The layout fills the CTA's shared memory to the last kilobyte; the launch sizes the dynamic window from the kernel's
+    // static size.  Should the window nevertheless start somewhere else than assumed, do nothing rather than run over it.
+    uint32_t dyn;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+    if ((uint32_t)(smem - smem_raw) + (uint32_t)SMEM_USED > dyn) {      // uniform over the grid
+      if (tid == 0) {
+        if (p.status) atomicExch(p.status, HA_DEV_BAD_LAUNCH);
+        if (p.status_host) {
+          *reinterpret_cast<volatile int32_t*>(p.status_host) = HA_DEV_BAD_LAUNCH;
+          __threadfence_system();
+        }
+      }
+      return;
+    }
+  }
   auto bar = [&](int i) -> uint32_t { return smem_u32(&bars[i]); };
   if (tid == 0) {
     for (int i = 0; i < N_BARS; ++i) mbar_init(bar(i), bar_count(i));
@@ -175,12 +220,14 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
           HA_T_MARK(0)
           float* ldt = reinterpret_cast<float*>(smem + OFF_LD + y * 1024);
           if (x == 0 && s == 0) {
-            // lse / delta of the query tile have landed: scale them once for all of the item's pairs (256 values, one per
-            // elementwise thread), then meet on a barrier of their own
+            // lse / delta of the query tile have landed: scale them once for all of the item's pairs.  Each group scales
+            // what it reads itself (its 32 columns of either half: 64 lse and 64 delta values, one per thread) and meets on
+            // a barrier of its own, so that neither group waits for the other here.
             if (!(ok = wait(B_QD_FULL + y, it & 1))) break;
-            ldt[tid] *= tid < TILE ? -LOG2E : -p.scale;
-            mbar_arrive(bar(B_LDT + y));
-            if (!(ok = wait(B_LDT + y, it & 1))) break;
+            const int j = row & 63;
+            ldt[(row >> 6) * TILE + 64 * (j >> 5) + 32 * g + (j & 31)] *= row < 64 ? -LOG2E : -p.scale;
+            mbar_arrive(bar(B_LDT + 2 * y + g));
+            if (!(ok = wait(B_LDT + 2 * y + g, it & 1))) break;
           }
           HA_T_MARK(1)
           if (pair >= 2 && !(ok = wait(B_DS_FREE + (pair & 1), ((pair >> 1) - 1) & 1))) break;   // dQ of pair - 2 has read the buffer
@@ -190,36 +237,46 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
           const uint32_t tS = tmem + 128 * s + 32 * g + lane_sel, tDP = tS + 64;
           const float* ld = ldt + 64 * s + 32 * g;
           uint8_t* ds_row = smem + OFF_DS + (pair & 1) * 2 * TILE_B + s * TILE_B + row * 128;
-          uint32_t rs[32], rp[32];
-          tmem_ld32(tS, rs);
-          tmem_ld32(tDP, rp);
-          tmem_ld_fence(rs);
-          tmem_ld_fence(rp);
-          uint32_t pk[16], dk[16];
+          // 32 columns in two chunks of 16: few enough live registers that the compiler can keep several columns' chains
+          // in flight (with 32 at a time the loop was bound by the latency of one chain after the other); the second
+          // chunk's TMEM loads travel while the first is computed
+          uint32_t rs[2][16], rp[2][16];
+          tmem_ld16(tS, rs[0]);
+          tmem_ld16(tDP, rp[0]);
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            // four query columns: their (scaled) lse and delta, the same for every thread: broadcast reads
-            const ulonglong2 L = *reinterpret_cast<const ulonglong2*>(ld + i);
-            const ulonglong2 Dl = *reinterpret_cast<const ulonglong2*>(ld + TILE + i);
-            float p0, p1, p2, p3, d0, d1, d2, d3;
-            unpack_f2(ffma2(pack_u2(rs[i], rs[i + 1]), sc2, L.x), p0, p1);
-            unpack_f2(ffma2(pack_u2(rs[i + 2], rs[i + 3]), sc2, L.y), p2, p3);
-            p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
-            // ds = p * (dp - delta) * scale
-            unpack_f2(fmul2(pack_f2(p0, p1), ffma2(pack_u2(rp[i], rp[i + 1]), scl, Dl.x)), d0, d1);
-            unpack_f2(fmul2(pack_f2(p2, p3), ffma2(pack_u2(rp[i + 2], rp[i + 3]), scl, Dl.y)), d2, d3);
-            pk[i >> 1] = pack2<T>(p0, p1);
-            pk[(i >> 1) + 1] = pack2<T>(p2, p3);
-            dk[i >> 1] = pack2<T>(d0, d1);
-            dk[(i >> 1) + 1] = pack2<T>(d2, d3);
+          for (int c = 0; c < 2; ++c) {
+            tmem_ld_fence16(rs[c]);
+            tmem_ld_fence16(rp[c]);
+            if (c == 0) {
+              tmem_ld16(tS + 16, rs[1]);
+              tmem_ld16(tDP + 16, rp[1]);
+            }
+            uint32_t pk[8], dk[8];
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              // four query columns: their (scaled) lse and delta, the same for every thread: broadcast reads
+              const ulonglong2 L = *reinterpret_cast<const ulonglong2*>(ld + c * 16 + i);
+              const ulonglong2 Dl = *reinterpret_cast<const ulonglong2*>(ld + TILE + c * 16 + i);
+              float p0, p1, p2, p3, d0, d1, d2, d3;
+              unpack_f2(ffma2(pack_u2(rs[c][i], rs[c][i + 1]), sc2, L.x), p0, p1);
+              unpack_f2(ffma2(pack_u2(rs[c][i + 2], rs[c][i + 3]), sc2, L.y), p2, p3);
+              p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
+              // ds = p * (dp - delta) * scale
+              unpack_f2(fmul2(pack_f2(p0, p1), ffma2(pack_u2(rp[c][i], rp[c][i + 1]), scl, Dl.x)), d0, d1);
+              unpack_f2(fmul2(pack_f2(p2, p3), ffma2(pack_u2(rp[c][i + 2], rp[c][i + 3]), scl, Dl.y)), d2, d3);
+              pk[i >> 1] = pack2<T>(p0, p1);
+              pk[(i >> 1) + 1] = pack2<T>(p2, p3);
+              dk[i >> 1] = pack2<T>(d0, d1);
+              dk[(i >> 1) + 1] = pack2<T>(d2, d3);
+            }
+            // P^T / dS^T of the chunk (8 packed columns) over columns this thread has already consumed
+            tmem_st8(tS + c * 8, pk);
+            tmem_st8(tDP + c * 8, dk);
+            // dS^T row to shared memory: slab s, this key row, 16-byte chunks 4 g + 2 c, 4 g + 2 c + 1
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              *reinterpret_cast<uint4*>(ds_row + ((((g * 4 + c * 2 + j) ^ row) & 7) << 4)) = make_uint4(dk[4 * j], dk[4 * j + 1], dk[4 * j + 2], dk[4 * j + 3]);
           }
-          // P^T / dS^T (16 packed columns) over the first half of the 32 columns this thread has just read
-          tmem_st16(tS, pk);
-          tmem_st16(tDP, dk);
-          // dS^T row to shared memory: slab s, this key row, 16-byte chunks 4 g .. 4 g + 3
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<uint4*>(ds_row + ((((g * 4 + j) ^ row) & 7) << 4)) = make_uint4(dk[4 * j], dk[4 * j + 1], dk[4 * j + 2], dk[4 * j + 3]);
           HA_T_MARK(3)
           tmem_st_wait();
           fence_async_smem();       // the dS rows are read by the tensor core (async proxy)
@@ -232,7 +289,7 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
         }
       }
     }
-    HA_T_DUMP(8, (int)blockIdx.x * 4 + g, row == 0)
+    HA_T_DUMP(8, (int)blockIdx.x * 8 + g, row == 0)
   } else if (warp < 12) {
     // =====================================================================================================
     // drain group: finished accumulators -> global memory
@@ -258,16 +315,41 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
         for (int i = 0; i < 16; i += 2) w[c * 8 + (i >> 1)] = pack2<T>(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
       }
     };
-    auto put = [&](const uint32_t (&w)[32], T* dst, float* acc, bool typed) {
+    // A row leaves through the copy engine: the thread writes its packed row into its own 128 bytes of a staging tile and
+    // issues ONE bulk copy (typed rows) or two bulk fp32 additions of half a row each (accumulators, slot buffers).  Stores
+    // and reductions issued by the lanes themselves touch 32 different lines per instruction (a lane owns a row), and kept
+    // the load / store unit -- which also serves the shared-memory traffic of every other role -- busy enough to slow the
+    // whole CTA by a third.  Chunk i of the row is written by instruction (i - row) & 7, so that the eight lanes of a
+    // quarter warp hit different banks while the row stays contiguous for the copy.
+    uint8_t* st_row = smem + OFF_ST + row * 128;
+    const uint32_t st_addr = smem_u32(st_row);
+    const int rot = row & 7;
+    auto put = [&](uint32_t (&w)[32], T* dst, float* acc, bool typed) {
       if (typed) {
-        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        bws_rot8<4>(w, rot);
+        bws_bulk_wait_read();
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) d4[i >> 2] = make_uint4(w[i], w[i + 1], w[i + 2], w[i + 3]);
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<uint4*>(st_row + (((i + rot) & 7) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        fence_async_smem();
+        bws_bulk_store(dst, st_addr, 128);
+        bws_bulk_commit();
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 lo = unpack2<T>(w[i]), hi = unpack2<T>(w[i + 1]);
-          bws_red_add_v4(acc + 2 * i, lo.x, lo.y, hi.x, hi.y);
+        for (int h = 0; h < 2; ++h) {
+          uint32_t u[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) u[i] = w[16 * h + i];
+          bws_rot8<2>(u, rot);
+          bws_bulk_wait_read();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float2 lo = unpack2<T>(u[2 * i]), hi = unpack2<T>(u[2 * i + 1]);
+            *reinterpret_cast<float4*>(st_row + (((i + rot) & 7) << 4)) = make_float4(lo.x, lo.y, hi.x, hi.y);
+          }
+          fence_async_smem();
+          bws_bulk_add_f32(acc + 32 * h, st_addr, 128);
+          bws_bulk_commit();
         }
       }
     };
@@ -334,7 +416,8 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
       }
       if (ok) ok = drain_dq(1);
     }
-    HA_T_DUMP(8, (int)blockIdx.x * 4 + 2, row == 0)
+    bws_bulk_wait_all();       // nothing of this thread is in flight when the CTA retires
+    HA_T_DUMP(8, (int)blockIdx.x * 8 + 2, row == 0)
   } else {
     // warps 12 .. 19: three loader warps and five MMA-issuing threads (two warpgroups of 64 registers)
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
@@ -401,7 +484,7 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
             for (int q = 0; q < 4; ++q) krows[q] = knext[q];
           }
         }
-        HA_T_DUMP(8, (int)blockIdx.x * 4 + 3, lane == 0 && warp == 12)
+        HA_T_DUMP(8, (int)blockIdx.x * 8 + 3, lane == 0 && warp == 12)
       } else {
         for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++it) {
           const int seg = item / blocks_per_seg, blk = item - seg * blocks_per_seg;
@@ -416,7 +499,9 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
             int qrows[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) qrows[q] = p.q_idx[(long long)seg * p.m_q + (2 * blk + y) * TILE + q * 32 + lane];
+            HA_T_MARK(0)
             if (it >= 1 && !(ok = wait(B_QD_EMPTY + y, (it - 1) & 1))) break;
+            HA_T_MARK(1)
             bws_gather_tile(s_base + OFF_QD + y * 2 * TILE_B, qbase, p.q_sn, qrows, lane);
             bws_gather_tile(s_base + OFF_QD + y * 2 * TILE_B + TILE_B, gbase, p.do_sn, qrows, lane);
 #pragma unroll
@@ -426,6 +511,7 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
               cp_async4(dst + 512, delta_base + qrows[q]);
             }
             push(B_QD_FULL + y);
+            HA_T_MARK(2)
           }
           // The next item's query-side rows: pulled into L2 now, so that the copies issued when their stages come free
           // (at the very end of this item) find them there instead of in DRAM.
@@ -443,6 +529,7 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
             }
           }
         }
+        HA_T_DUMP(8, (int)blockIdx.x * 8 + 7, lane == 0)
       }
       cp_async_commit();
       cp_async_wait<0>();      // nothing of this warp is in flight when the CTA retires
@@ -490,16 +577,20 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
           if (x == (uint32_t)nX - 1 && s == 1) mma_commit(bar(B_QD_EMPTY + y));      // ... and of the Q / dO stage
           HA_T_MARK(3)
         }
-        HA_T_DUMP(8, (int)blockIdx.x * 4 + 3, false)
+        HA_T_DUMP(8, (int)blockIdx.x * 8 + 4, warp == 15)
       } else if (warp == 17 || warp == 18) {
         // dV += P^T dO (warp 17) / dK += dS^T Q (warp 18) over the half's 64 query rows: A in TMEM, B rows as MN-major
         const bool second = warp == 18;
         const uint32_t id_kv = mma_idesc(TILE, 64, AB, 0, 1);
+        HA_T_DECL(8)
         for (uint32_t hh = 0; hh < total && ok; ++hh) {
           const uint32_t r = hh % NH, x = r >> 2, y = (r >> 1) & 1, s = r & 1;
           const uint32_t pair = hh >> 1, xg = hh >> 2;
+          HA_T_MARK(0)
           if (!(ok = wait(B_P_READY + s, pair & 1))) break;
+          HA_T_MARK(1)
           if ((r & 3) == 0 && xg >= 1 && !(ok = wait(B_ACC_FREE, (xg - 1) & 1))) break;    // the accumulator restarts with the key tile
+          HA_T_MARK(2)
           fence_async_smem();
           tc_fence_after();
           const uint32_t sB = s_base + OFF_QD + y * 2 * TILE_B + s * (TILE_B / 2) + (second ? 0 : TILE_B);   // Q rows (dK) / dO rows (dV)
@@ -513,16 +604,22 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
           mma_commit(bar((second ? B_SF_P : B_SF_S) + s));
           if ((r & 3) == 3) mma_commit(bar(B_ACC_FULL));                            // the key tile's accumulator is complete
           if (x == (uint32_t)nX - 1 && s == 1) mma_commit(bar(B_QD_EMPTY + y));
+          HA_T_MARK(3)
         }
+        HA_T_DUMP(8, (int)blockIdx.x * 8 + 5, warp == 17)
       } else {
         // dQ_y += dS K over the pair's 128 keys: A = dS ([key][query] rows: MN-major), B = K rows as MN-major
         const uint32_t id_dq = mma_idesc(TILE, 64, AB, 1, 1);
         const uint32_t total_pairs = total >> 1;
+        HA_T_DECL(8)
         for (uint32_t pair = 0; pair < total_pairs && ok; ++pair) {
           const uint32_t r = (2 * pair) % NH, itc = (2 * pair) / NH, x = r >> 2, y = (r >> 1) & 1, xg = pair >> 1;
+          HA_T_MARK(0)
           // both halves of the pair have written their dS slabs
           if (!(ok = wait(B_DS_FULL + (pair & 1), (pair >> 1) & 1))) break;
+          HA_T_MARK(1)
           if (x == 0 && itc >= 1 && !(ok = wait(B_DQ_FREE + y, (itc - 1) & 1))) break;      // dQ restarts with the item
+          HA_T_MARK(2)
           fence_async_smem();
           tc_fence_after();
           const uint32_t sK = s_base + OFF_K + (xg % K_STAGES) * TILE_B;
@@ -534,7 +631,9 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
           mma_commit(bar(B_DS_FREE + (pair & 1)));
           if (x == (uint32_t)nX - 1) mma_commit(bar(B_DQ_FULL + y));                  // the query tile's dQ is complete
           if (y == 1) mma_commit(bar(B_K_EMPTY + xg % K_STAGES));                     // this thread's last read of the K tile
+          HA_T_MARK(3)
         }
+        HA_T_DUMP(8, (int)blockIdx.x * 8 + 6, true)
       }
     }
   }
@@ -576,10 +675,21 @@ int ws_attn_bwd(const ha_attn_params& p, cudaStream_t st) {
   if (items * 4 * (2 + p.sample_size / TILE) > 0x7fffffffLL) return HA_ERR_TOO_LARGE;
   const int sms = sm_count();
   const int grid = (int)(items < sms ? items : sms);
+  // The dynamic window is everything the CTA may have beyond the kernel's static variables; the tiles start at its first
+  // 1 KB boundary.
 #define HA_BWS_LAUNCH(TT)                                                                                                        \
   do {                                                                                                                           \
-    HA_SMEM_ATTR_ONCE(attn_tc_bwd_ws_kernel<TT>, bws::SMEM, "ha_attn_bwd smem attribute");                                      \
-    attn_tc_bwd_ws_kernel<TT><<<grid, bws::THREADS, bws::SMEM, st>>>(p, (int)items, blocks_per_seg);                             \
+    static int dyn_bytes = 0;                                                                                                    \
+    if (dyn_bytes == 0) {                                                                                                        \
+      cudaFuncAttributes fa;                                                                                                     \
+      HA_CUDA_OK(cudaFuncGetAttributes(&fa, attn_tc_bwd_ws_kernel<TT>), "ha_attn_bwd kernel attributes");                        \
+      const int stat = ((int)fa.sharedSizeBytes + 15) / 16 * 16;                                                                 \
+      const int pad = (1024 - stat % 1024) % 1024;                                                                               \
+      if (stat + pad + bws::SMEM_USED > bws::SMEM_LIMIT) return HA_ERR_CUDA;                                                     \
+      dyn_bytes = bws::SMEM_LIMIT - stat;                                                                                        \
+    }                                                                                                                            \
+    HA_SMEM_ATTR_ONCE(attn_tc_bwd_ws_kernel<TT>, dyn_bytes, "ha_attn_bwd smem attribute");                                      \
+    attn_tc_bwd_ws_kernel<TT><<<grid, bws::THREADS, dyn_bytes, st>>>(p, (int)items, blocks_per_seg);                             \
   } while (0)
   if (p.dtype == HA_BF16) HA_BWS_LAUNCH(__nv_bfloat16);
   else HA_BWS_LAUNCH(__half);

@@ -57,7 +57,8 @@ def _set_status(p, device):
 
 def _status_text(v):
     return {L.DEV_TIMEOUT: 'a device-side wait timed out',
-            L.DEV_BAD_INDEX: 'an index array holds a row outside its segment (index check)'}.get(v, 'the device reported a failure')
+            L.DEV_BAD_INDEX: 'an index array holds a row outside its segment (index check)',
+            L.DEV_BAD_LAUNCH: 'a kernel found its shared-memory window too small and did no work'}.get(v, 'the device reported a failure')
 
 
 def _raise_if_failed(dev_w, host_w):

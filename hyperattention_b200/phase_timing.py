@@ -22,7 +22,11 @@ ROLES = {0: ('elementwise group 0', ['wait S^T/dP^T ready', 'wait lse/delta (+ s
                                        'store-wait, fences, arrivals']),
          2: ('drain group', ['wait accumulators full', 'index loads, global stores / reductions', 'wait dQ full', 'dQ rows',
                              'accumulator -> registers (issuers blocked)']),
-         3: ('K loader warp', ['index loads, L2 prefetch', 'wait stage empty', 'issuing the copies of a tile'])}
+         3: ('K loader warp', ['index loads, L2 prefetch', 'wait stage empty', 'issuing the copies of a tile']),
+         4: ('S^T issuer', ['loop', 'wait stage columns free (dV of the previous pair)', 'wait K / Q tiles', 'fences, 4 MMAs, commits']),
+         5: ('dV issuer', ['loop', 'wait P^T ready', 'wait accumulator drained', 'fences, 4 MMAs, commits']),
+         6: ('dQ issuer', ['loop', 'wait dS slabs full', 'wait dQ drained', 'fences, 8 MMAs, commits']),
+         7: ('Q / dO loader warp', ['index loads, L2 prefetch', 'wait stage empty', 'issuing the copies of two tiles'])}
 
 
 def main():
@@ -49,7 +53,7 @@ def main():
         o.backward(do)
         torch.cuda.synchronize()
     n_cta = min(148, a.heads * a.seq_len // 256)
-    b = buf.view(4096, 16).cpu().float()[:n_cta * 4].view(n_cta, 4, 16)
+    b = buf.view(4096, 16).cpu().float()[:n_cta * 8].view(n_cta, 8, 16)
     for r, (name, phases) in ROLES.items():
         bb = b[:, r]
         tot = bb[:, :8].sum(1).mean().item()

@@ -27,7 +27,8 @@ enum {
   HA_ERR_TOO_LARGE = -5,    /* beyond a size limit of the entry point: a grid dimension (segments, work items), or the
                                built-in scratch array of ha_seg_sort_noalloc */
   HA_DEV_TIMEOUT = 1,       /* a bounded device-side wait gave up (written to the caller's status word) */
-  HA_DEV_BAD_INDEX = 2      /* HA_FLAG_CHECK_INDICES: q_idx / k_idx / sample_idx holds a row outside its segment */
+  HA_DEV_BAD_INDEX = 2,     /* HA_FLAG_CHECK_INDICES: q_idx / k_idx / sample_idx holds a row outside its segment */
+  HA_DEV_BAD_LAUNCH = 3     /* a kernel found its shared-memory window smaller than its layout needs and did no work */
 };
 
 enum { HA_BF16 = 0, HA_FP16 = 1, HA_FP32 = 2 };
