@@ -59,7 +59,7 @@ static int check_common(const ha_attn_params& p, bool backward) {
 }
 
 template <typename T>
-__global__ void bwd_finish_kernel(const ha_attn_params p, long long total) {
+__global__ void bwd_finish_kernel(const ha_attn_params p, long long total, const bool tiled) {
   // one thread per (segment, slot, 8 elements of dk | dv)
   const int cpr_k = p.d / 8, cpr = cpr_k + p.dv / 8;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -73,10 +73,22 @@ __global__ void bwd_finish_kernel(const ha_attn_params p, long long total) {
   const bool is_k = c < cpr_k;
   const int w = is_k ? p.d : p.dv, e0 = (is_k ? c : c - cpr_k) * 8;
   T* out = (is_k ? (T*)p.dk_out : (T*)p.dv_out) + out_row * w + e0;
-  const float* acc = (is_k ? p.dk_sacc : p.dv_sacc) + (kseg_of(p, seg) * p.sample_size + slot) * w + e0;
+  // Layout of the slot buffers: [slot][w] rows, or -- written by the warp-specialised kernel (w = 64) -- per tile of 128
+  // slots two halves of [128 rows][32 floats], the 16-byte chunks of a row XOR-swizzled by the row: the layout of that
+  // kernel's staging tile.
+  const float* accb = (is_k ? p.dk_sacc : p.dv_sacc) + kseg_of(p, seg) * p.sample_size * w;
+  float4 a0, a1;
+  if (tiled) {
+    const float* rowp = accb + (long long)(slot / TILE) * (TILE * 64) + (e0 / 32) * (TILE * 32) + (slot % TILE) * 32;
+    const int c = (e0 % 32) / 4;
+    a0 = *reinterpret_cast<const float4*>(rowp + ((c ^ (slot & 7)) << 2));
+    a1 = *reinterpret_cast<const float4*>(rowp + (((c + 1) ^ (slot & 7)) << 2));
+  } else {
+    a0 = *reinterpret_cast<const float4*>(accb + (long long)slot * w + e0);
+    a1 = *reinterpret_cast<const float4*>(accb + (long long)slot * w + e0 + 4);
+  }
   uint4 raw = *reinterpret_cast<const uint4*>(out);
   T* v = reinterpret_cast<T*>(&raw);
-  const float4 a0 = *reinterpret_cast<const float4*>(acc), a1 = *reinterpret_cast<const float4*>(acc + 4);
   const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
   for (int j = 0; j < 8; ++j) v[j] = from_f32<T>(to_f32<T>(v[j]) + a[j]);
@@ -191,8 +203,9 @@ int ha_attn_bwd_finish(const ha_attn_params* p, void* stream) {
   if (total == 0) return HA_OK;
   if ((total + 255) / 256 > 0x7fffffffLL) return HA_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
-  if (p->dtype == HA_BF16) bwd_finish_kernel<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(*p, total);
-  else bwd_finish_kernel<__half><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(*p, total);
+  const bool tiled = !(p->flags & HA_FLAG_FORCE_SIMT) && ws_bwd_supported(*p);     // which kernel filled the slot buffers
+  if (p->dtype == HA_BF16) bwd_finish_kernel<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(*p, total, tiled);
+  else bwd_finish_kernel<__half><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(*p, total, tiled);
   HA_LAUNCHED("ha_attn_bwd_finish");
   return HA_OK;
 }

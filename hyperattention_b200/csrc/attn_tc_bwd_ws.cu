@@ -38,16 +38,16 @@
 namespace ha {
 
 namespace bws {
-constexpr int D = 64, DV = 64;
+constexpr int D = 64;
 constexpr int TILE_B = TILE * 64 * 2;                          // one 128 x 64 tile of 2-byte elements
-constexpr int K_STAGES = 3, V_STAGES = 2;                      // dQ reads K a pair or two after S^T has: K gets the deeper ring
+constexpr int K_STAGES = 2, V_STAGES = 2;
 constexpr int OFF_K = 0;                                       // K ring
 constexpr int OFF_V = OFF_K + K_STAGES * TILE_B;               // V ring
 constexpr int OFF_QD = OFF_V + V_STAGES * TILE_B;              // stage y (query tile y of the item): Q, then dO
 constexpr int OFF_DS = OFF_QD + 2 * 2 * TILE_B;                // two buffers (pairs alternate) of two slabs (column halves)
 constexpr int OFF_LD = OFF_DS + 2 * 2 * TILE_B;                // per query-tile stage: lse[128], delta[128] (fp32)
-constexpr int OFF_ST = OFF_LD + 2 * 1024;                      // staging tile of the drain group: 128 rows x 128 bytes
-constexpr int SMEM_USED = OFF_ST + TILE * 128;                 // from the 1024-byte aligned base
+constexpr int OFF_ST = OFF_LD + 2 * 1024;                      // two staging tiles of the drain group: 128 rows x 128 bytes
+constexpr int SMEM_USED = OFF_ST + 2 * TILE * 128;             // from the 1024-byte aligned base
 constexpr int SMEM_LIMIT = 227 * 1024;                         // per CTA, static + dynamic
 constexpr int THREADS = 640;
 constexpr int COL_DV = 256, COL_DK = 320, COL_DQ = 384;
@@ -70,7 +70,9 @@ enum {
   B_DS_FULL = 32,    // 2 x 512: both halves' dS slabs of a pair are in the buffer (every elementwise thread, twice)
   B_ACC_FULL = 34,   // 2: dV and dK of a key tile complete
   B_ACC_FREE = 35,   // 128: ... drained
-  N_BARS = 36
+  B_ST_FULL = 36,    // 128: every drain thread has written its row of staging tile B (whole-tile additions)
+  B_ST_FREE = 37,    // 1: the copy engine has read the tile
+  N_BARS = 38
 };
 __device__ __forceinline__ int bar_count(int i) {
   if (i < B_K_EMPTY) return 32;
@@ -84,30 +86,12 @@ __device__ __forceinline__ int bar_count(int i) {
   if (i < B_DQ_FREE) return 1;          // stage-free (S, P), dS-free, dQ-full
   if (i < B_DS_FULL) return 128;        // dQ-free, pre-scaled lse / delta
   if (i < B_ACC_FULL) return 512;
-  return i == B_ACC_FULL ? 2 : 128;
+  if (i == B_ACC_FULL) return 2;
+  return i >= B_ST_FREE ? 1 : 128;
 }
 }  // namespace bws
 
-// Rotates the eight chunks (CW words each) of a row held in registers: afterwards chunk i is what chunk (i + rot) & 7 was.
-// Register arrays cannot be indexed by a run-time value: three conditional steps of 1, 2 and 4 chunks, selects only.
-template <int CW>
-__device__ __forceinline__ void bws_rot8(uint32_t (&w)[8 * CW], int rot) {
-#pragma unroll
-  for (int st = 1; st < 8; st <<= 1) {
-    const bool on = (rot & st) != 0;
-    uint32_t t[8 * CW];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-      for (int k = 0; k < CW; ++k) t[i * CW + k] = on ? w[((i + st) & 7) * CW + k] : w[i * CW + k];
-#pragma unroll
-    for (int i = 0; i < 8 * CW; ++i) w[i] = t[i];
-  }
-}
-// Bulk copies shared -> global of the copy engine (a thread's own row of the staging tile): plain store and fp32 add.
-__device__ __forceinline__ void bws_bulk_store(void* dst, uint32_t src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
-}
+// Bulk fp32 addition shared -> global by the copy engine (a whole staging tile).
 __device__ __forceinline__ void bws_bulk_add_f32(float* dst, uint32_t src, uint32_t bytes) {
   asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
 }
@@ -199,10 +183,10 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
     // elementwise groups: P^T = exp2(S^T scale log2e - lse log2e), dS^T = P^T (dP^T - delta) scale
     // =====================================================================================================
     // Register budget.  What setmaxnreg redistributes is the CTA's own allocation at launch: 640 threads x 96 registers =
-    // 61440 (not the SM's whole file); a request beyond it waits forever.  The two elementwise groups go up to 120, the
-    // drain group to 112 (it holds two packed accumulator rows), the two warpgroups of the loader and the MMA issuers go
-    // down to 64: 2 x 128 x 120 + 128 x 112 + 2 x 128 x 64 = 61440.
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
+    // 61440 (not the SM's whole file); a request beyond it waits forever.  The two elementwise groups go up to 104, the
+    // drain group to 144 (it holds two packed accumulator rows while it writes them out), the two warpgroups of the
+    // loaders and the MMA issuers go down to 64: 2 x 128 x 104 + 128 x 144 + 2 x 128 x 64 = 61440.
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
     const int g = warp >> 2, gw = warp & 3, row = tid & 127;
     const uint32_t lane_sel = (uint32_t)(gw * 32) << 16;
     const uint64_t sc2 = pack_f2(p.scale * LOG2E, p.scale * LOG2E), scl = pack_f2(p.scale, p.scale);
@@ -294,7 +278,7 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
     // =====================================================================================================
     // drain group: finished accumulators -> global memory
     // =====================================================================================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 144;");
     const int gw = warp & 3, row = tid & 127;
     const uint32_t lane_sel = (uint32_t)(gw * 32) << 16;
     bool ok = true;
@@ -315,41 +299,82 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
         for (int i = 0; i < 16; i += 2) w[c * 8 + (i >> 1)] = pack2<T>(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
       }
     };
-    // A row leaves through the copy engine: the thread writes its packed row into its own 128 bytes of a staging tile and
-    // issues ONE bulk copy (typed rows) or two bulk fp32 additions of half a row each (accumulators, slot buffers).  Stores
-    // and reductions issued by the lanes themselves touch 32 different lines per instruction (a lane owns a row), and kept
-    // the load / store unit -- which also serves the shared-memory traffic of every other role -- busy enough to slow the
-    // whole CTA by a third.  Chunk i of the row is written by instruction (i - row) & 7, so that the eight lanes of a
-    // quarter warp hit different banks while the row stays contiguous for the copy.
-    uint8_t* st_row = smem + OFF_ST + row * 128;
-    const uint32_t st_addr = smem_u32(st_row);
+    // How rows leave.  A lane owns a row, and stores or reductions issued row by row touch 32 different lines per
+    // instruction: they kept the load / store unit -- which also serves the shared-memory traffic of every other role --
+    // busy enough to slow the whole CTA by a third.  So:
+    //  * rows with a destination of their own (typed dK / dV / dQ rows, fp32 accumulator rows) are transposed through the
+    //    warp's 4 KB of staging tile A (rows written with their 16-byte chunks XOR-swizzled, read back four whole rows per
+    //    instruction) and leave as coalesced stores / reductions: eight lanes cover the 128 contiguous bytes of a row;
+    //  * the sampled rows' slot buffers are laid out as staging tile B is ([key tile][half][row][32 floats], chunks
+    //    swizzled the same way), so half an accumulator of all 128 rows is ONE bulk fp32 addition of 16 KB by one thread.
+    //    (Bulk copies of single rows were tried for everything: the copy engine accepts one every ~15 cycles, and 1800
+    //    of them per work item made the drain group the bottleneck of the CTA.)
     const int rot = row & 7;
-    auto put = [&](uint32_t (&w)[32], T* dst, float* acc, bool typed) {
+    uint8_t* my_row_a = smem + OFF_ST + row * 128;
+    const uint8_t* warp_rows = smem + OFF_ST + (row & ~31) * 128;
+    uint8_t* my_row_b = smem + OFF_ST + TILE * 128 + row * 128;
+    uint32_t tile_ops = 0;       // whole-tile additions issued so far
+    bool tile_pending = false;   // ... and the last one may still be reading tile B
+    auto put_tile = [&](const uint32_t (&w)[32], float* acc_tile) -> bool {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        HA_T_MARK(1)
+        if (tile_pending && !wait(B_ST_FREE, (tile_ops - 1) & 1)) return false;
+        HA_T_MARK(5)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 lo = unpack2<T>(w[16 * h + 2 * i]), hi = unpack2<T>(w[16 * h + 2 * i + 1]);
+          *reinterpret_cast<float4*>(my_row_b + ((i ^ rot) << 4)) = make_float4(lo.x, lo.y, hi.x, hi.y);
+        }
+        HA_T_MARK(1)
+        fence_async_smem();
+        HA_T_MARK(6)
+        mbar_arrive(bar(B_ST_FULL));
+        if (row == 0) {
+          if (!wait(B_ST_FULL, tile_ops & 1)) return false;
+          bws_bulk_add_f32(acc_tile + h * (TILE * 32), smem_u32(smem + OFF_ST + TILE * 128), TILE * 128);
+          bws_bulk_commit();
+          bws_bulk_wait_read();
+          mbar_arrive(bar(B_ST_FREE));
+        }
+        ++tile_ops;
+        tile_pending = true;
+        HA_T_MARK(7)
+      }
+      return true;
+    };
+    // `rid`: this lane's destination row in dst (typed rows of 64 elements) or acc (fp32 rows of 64)
+    auto put = [&](const uint32_t (&w)[32], T* dst, float* acc, uint32_t rid, bool typed) {
       if (typed) {
-        bws_rot8<4>(w, rot);
-        bws_bulk_wait_read();
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<uint4*>(st_row + (((i + rot) & 7) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
-        fence_async_smem();
-        bws_bulk_store(dst, st_addr, 128);
-        bws_bulk_commit();
+          *reinterpret_cast<uint4*>(my_row_a + ((i ^ rot) << 4)) = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int rl = 4 * j + (lane >> 3), c = lane & 7;
+          const uint4 v = *reinterpret_cast<const uint4*>(warp_rows + rl * 128 + ((c ^ (rl & 7)) << 4));
+          const size_t rr = __shfl_sync(0xffffffffu, rid, rl);
+          *reinterpret_cast<uint4*>(dst + rr * 64 + c * 8) = v;
+        }
+        __syncwarp();
       } else {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          uint32_t u[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) u[i] = w[16 * h + i];
-          bws_rot8<2>(u, rot);
-          bws_bulk_wait_read();
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float2 lo = unpack2<T>(u[2 * i]), hi = unpack2<T>(u[2 * i + 1]);
-            *reinterpret_cast<float4*>(st_row + (((i + rot) & 7) << 4)) = make_float4(lo.x, lo.y, hi.x, hi.y);
+            const float2 lo = unpack2<T>(w[16 * h + 2 * i]), hi = unpack2<T>(w[16 * h + 2 * i + 1]);
+            *reinterpret_cast<float4*>(my_row_a + ((i ^ rot) << 4)) = make_float4(lo.x, lo.y, hi.x, hi.y);
           }
-          fence_async_smem();
-          bws_bulk_add_f32(acc + 32 * h, st_addr, 128);
-          bws_bulk_commit();
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int rl = 4 * j + (lane >> 3), c = lane & 7;
+            const float4 v = *reinterpret_cast<const float4*>(warp_rows + rl * 128 + ((c ^ (rl & 7)) << 4));
+            const size_t rr = __shfl_sync(0xffffffffu, rid, rl);
+            bws_red_add_v4(acc + rr * 64 + 32 * h + c * 4, v.x, v.y, v.z, v.w);
+          }
+          __syncwarp();
         }
       }
     };
@@ -375,7 +400,7 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
         grab(tmem + COL_DQ + y * D + lane_sel, w);
         tc_fence_before();
         mbar_arrive(bar(B_DQ_FREE + y));
-        put(w, (T*)p.dq_out + r * D, p.dq_acc + r * D, dq_direct);
+        put(w, (T*)p.dq_out, p.dq_acc, (uint32_t)r, dq_direct);
         HA_T_MARK(3)
         return true;
       };
@@ -392,15 +417,13 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
         // block's share of the row's sum, reduced into the slot buffers (typed outputs) / the accumulators
         const bool typed = kv_direct && !sampled;
         const long long r = si.khead0 + si.k_row0 + krow;
-        float* acc_k = nullptr;
-        float* acc_v = nullptr;
+        float* acc_k = p.dk_acc;
+        float* acc_v = p.dv_acc;
         if (kv_direct && sampled) {
-          const long long slot = kseg_of(p, seg) * p.sample_size + (x - 2) * TILE + row;
-          acc_k = p.dk_sacc + slot * D;
-          acc_v = p.dv_sacc + slot * DV;
-        } else if (!kv_direct) {
-          acc_k = p.dk_acc + r * D;
-          acc_v = p.dv_acc + r * DV;
+          // the sampled tile's 128 x 64 block of the slot buffer
+          const long long tile_at = (kseg_of(p, seg) * p.sample_size + (x - 2) * TILE) * D;
+          acc_k = p.dk_sacc + tile_at;
+          acc_v = p.dv_sacc + tile_at;
         }
         {
           uint32_t wv[32], wk[32];
@@ -409,8 +432,12 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
           tc_fence_before();
           mbar_arrive(bar(B_ACC_FREE));
           HA_T_MARK(4)
-          put(wv, (T*)p.dv_out + r * DV, acc_v, typed);
-          put(wk, (T*)p.dk_out + r * D, acc_k, typed);
+          if (kv_direct && sampled) {
+            ok = put_tile(wv, acc_v) && put_tile(wk, acc_k);
+          } else {
+            put(wv, (T*)p.dv_out, acc_v, (uint32_t)r, typed);
+            put(wk, (T*)p.dk_out, acc_k, (uint32_t)r, typed);
+          }
         }
         krow = krow_next;
       }

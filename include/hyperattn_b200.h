@@ -165,8 +165,9 @@ typedef struct {
   /* backward, HA_MODE_HYPER on the tensor-core kernel only (ha_attn_bwd_uses_tensor_cores): direct dK/dV.  Every key
    * row's block part is complete inside one work item, so it is stored straight into dk_out / dv_out (dtype rows,
    * [B,H,n,d] / [B,H,n,dv] contiguous, every row of every segment written); the sampled rows' extra terms are summed in
-   * the small slot-indexed fp32 buffers dk_sacc / dv_sacc ([B*H*segs_per_head][sample_size][d] / [...][dv], zeroed by
-   * the caller) and added by ha_attn_bwd_finish.  dk_acc / dv_acc are not used then.  sample_idx rows must be distinct.
+   * the small slot-indexed fp32 buffers dk_sacc / dv_sacc (B*H*segs_per_head * sample_size * d / ... * dv floats, zeroed
+   * by the caller; the order of the floats inside is the library's own) and added by ha_attn_bwd_finish, which must get
+   * the same parameters.  dk_acc / dv_acc are not used then.  sample_idx rows must be distinct.
    * Same arithmetic as the reference, whose sampled-column kernel adds onto the dk / dv its block kernel stored
    * (src/hyper_attn_triton.py:399-506, :517-665). */
   void *dk_out, *dv_out;
