@@ -20,9 +20,9 @@ ROLES = {0: ('elementwise group 0', ['wait S^T/dP^T ready', 'wait lse/delta (+ s
                                        'store-wait, fences, arrivals']),
          1: ('elementwise group 1', ['wait S^T/dP^T ready', 'wait lse/delta (+ scaling)', 'wait dS buffer free', 'loads + math + stores',
                                        'store-wait, fences, arrivals']),
-         2: ('drain group', ['wait accumulators full', 'index loads, rotation, staging writes', 'wait dQ full', 'dQ rows',
-                             'accumulator -> registers (issuers blocked)', 'wait staging row / tile free', 'proxy fence',
-                             'issuing the bulk copies (thread 0 of the group: + their read)']),
+         2: ('drain group', ['wait accumulators full', 'index loads, staging writes, coalesced stores / reductions', 'wait dQ full', 'dQ rows',
+                             'accumulator -> registers (issuers blocked)', 'wait staging tile free (whole-tile additions)', 'proxy fence',
+                             'whole-tile additions: barrier, issue (thread 0 of the group: + the read of the tile)']),
          3: ('K loader warp', ['index loads, L2 prefetch', 'wait stage empty', 'issuing the copies of a tile']),
          4: ('S^T issuer', ['loop', 'wait stage columns free (dV of the previous pair)', 'wait K / Q tiles', 'fences, 4 MMAs, commits']),
          5: ('dV issuer', ['loop', 'wait P^T ready', 'wait accumulator drained', 'fences, 4 MMAs, commits']),
