@@ -289,14 +289,17 @@ __global__ void __launch_bounds__(bws::THREADS, 1) attn_tc_bwd_ws_kernel(const h
     // tensors' dtype in registers (32 packed words), the "free" barrier is signalled, and only then do the words go out --
     // as one typed row (128 contiguous bytes), or, unpacked again, as fp32 reductions.  (What is added into an fp32
     // accumulator or slot buffer is therefore rounded per work item, as the typed rows are.)
+    // (both halves of the row are requested before the one wait: the issuers are blocked for as long as this takes)
     auto grab = [&](uint32_t taddr, uint32_t (&w)[32]) {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(taddr, r0);
+      tmem_ld32(taddr + 32, r1);
+      tmem_ld_fence(r0);
+      tmem_ld_fence(r1);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c * 16, r);
-        tmem_ld_fence16(r);
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) w[c * 8 + (i >> 1)] = pack2<T>(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+      for (int i = 0; i < 32; i += 2) {
+        w[i >> 1] = pack2<T>(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+        w[16 + (i >> 1)] = pack2<T>(__uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
       }
     };
     // How rows leave.  A lane owns a row, and stores or reductions issued row by row touch 32 different lines per
