@@ -18,8 +18,9 @@
 //     every half.  Both groups work on the same half, so a half's elementwise phase is short and the other TMEM stage
 //     is in its tensor phases meanwhile.
 //   * drain group (128 threads, thread = TMEM lane): dK / dV rows of a finished key tile, dQ rows of a finished query
-//     tile -> global memory (typed rows, or fp32 reductions into accumulators / slot buffers).
-//   * three loader warps, one per operand stream (K tiles: ring of three; V tiles: ring of two; (Q, dO, lse, delta): one
+//     tile -> global memory.  Rows are transposed through a staging tile and leave coalesced (typed rows, fp32
+//     reductions into accumulators); the sampled rows' slot sums leave as whole-tile bulk additions of the copy engine.
+//   * three loader warps, one per operand stream (K tiles: ring of two; V tiles: ring of two; (Q, dO, lse, delta): one
 //     stage per query tile of the item): rows gathered by index with cp.async; the copies signal the "full" barriers
 //     themselves, a loader only waits for free buffers and runs ahead.  The rows of the next tile are pulled into L2 first.
 //   * five MMA-issuing threads (one per warp), one product each: S^T, dP^T, dV, dK of every half, dQ of every pair.
