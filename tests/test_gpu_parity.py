@@ -300,6 +300,8 @@ def test_module_uniform_sampling_mode(ha):
     (512, 64, 256, 0, False, False, torch.bfloat16),          # direct dq without a sampled launch
     (1152, 64, 256, 256, False, False, torch.float16),        # 9 query tiles: a last chunk of one tile; odd block count -> level 1
     (2304, 64, 256, 256, False, False, torch.bfloat16),       # 18 query tiles: chunks of 8, 8, 2
+    (768, 64, 256, 128, False, False, torch.bfloat16),        # one sampled tile: slot buffers of a single 128-row tile
+    (768, 64, 256, 384, False, False, torch.bfloat16),        # three sampled tiles
     (1024, 64, 256, 256, False, True, torch.bfloat16),
 ])
 def test_direct_dk_dv_matches_fp32_accumulators(ha, cfg):
@@ -324,6 +326,33 @@ def test_direct_dk_dv_matches_fp32_accumulators(ha, cfg):
     assert rel(direct[0], legacy[0]) < 1e-3
     for g, w in zip(direct[1:], legacy[1:]):
         assert g.dtype == dtype and rel(g, w) < 6e-3
+
+
+@pytest.mark.parametrize('shape', [(1, 2, 1024, 256), (2, 3, 2048, 256), (1, 2, 1024, 0), (1, 1, 512, 128), (1, 40, 2048, 256), (1, 3, 768, 384)])
+@pytest.mark.parametrize('direct', [True, False])
+def test_warp_specialised_backward_matches_earlier_kernel(ha, shape, direct):
+    """attn_tc_bwd_ws_kernel (rows leave transposed through a staging tile; sampled rows as whole-tile bulk additions into
+    slot buffers of its own layout) against the earlier backward kernel (HA_FLAG_NO_WS) on the same inputs, with typed
+    outputs and with fp32 accumulators: the same sums in a different order and with one rounding of the partials"""
+    from hyperattention_b200 import ops, _lib as L
+    B, H, n, S = shape
+    g = torch.Generator(device='cuda').manual_seed(7)
+    q, k, v, do = [torch.randn(B, H, n, 64, device='cuda', generator=g).bfloat16() for _ in range(4)]
+    proj = torch.randn(64, 8, device='cuda', generator=g)
+    codes = torch.empty(2, B, H, n, dtype=torch.int32, device='cuda')
+    ops.lsh_hash(q, proj, codes[0])
+    ops.lsh_hash(k, proj, codes[1])
+    idx = ops.seg_sort(codes.view(2 * B * H, n), 8)
+    qi, ki = idx[:B * H].view(B, H, n), idx[B * H:].view(B, H, n)
+    o, lse = ops.hyper_attn_func(T(q), T(k), T(v), T(qi), T(ki), 256, S)
+    delta = (o.float() * T(do).float()).sum(-1).transpose(1, 2).contiguous()
+    outs = []
+    for flags in (L.FLAG_NO_WS, 0):
+        r = ops.hyper_bwd(T(q), T(k), T(v), qi.view(B * H, n), ki.view(B * H, n), None, o, lse, T(do), delta, 256, S, 0.125, flags, None, direct)
+        torch.cuda.synchronize()
+        outs.append([t.clone() for t in r])
+    for a_, b_ in zip(outs[1], outs[0]):
+        assert rel(a_, b_) < 4e-3
 
 
 @pytest.mark.parametrize('tag', ['plain', 'smooth', 'nosamp', 'd128', 'd128bwd', 's256bwd'])
