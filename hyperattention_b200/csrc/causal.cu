@@ -162,6 +162,78 @@ struct SavedLayout {
   }
 };
 
+// The merges of the causal schedule as one pass over the stored parts (training calls keep every part's (o, lse) for the
+// backward anyway): a row starts from its leaf part and takes in, from the deepest rectangle up, every rectangle part
+// whose query half it lies in -- the arithmetic of the attention kernels' merging epilogue (add_self_attentions,
+// utils.py:82-88 of the reference: weights rounded to the tensors' dtype, the merged row rounded after every step), in
+// the same order.  The rectangle launches then run as plain calls that write their part and read nothing back, which
+// costs them a third less time than merging in their epilogue (old rows gathered, two outputs stored).
+// One lane per 16-byte chunk of a row; part = depth, leaves last, as in the saved layout.
+template <typename T>
+__global__ void __launch_bounds__(256) merge_parts_kernel(const uint8_t* __restrict__ parts0, long long part_stride_bytes, long long lse_off_bytes,
+                                                          int levels, int n, int lpr, T* __restrict__ o, float* __restrict__ lse,
+                                                          long long total_rows, int exact) {
+  const int lane = threadIdx.x & 31;
+  const int rpw = 32 / lpr, chunk = lane % lpr, sub = lane / lpr;
+  const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int dv = lpr * 8;
+  for (long long base = warp_id * rpw; base < total_rows; base += n_warps * rpw) {
+    const long long row = base + sub;
+    if (row >= total_rows) continue;
+    const int i = (int)(row % n);
+    auto part_row = [&](int part) { return __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(parts0 + part * part_stride_bytes) + row * dv + chunk * 8)); };
+    auto part_lse = [&](int part) { return __ldg(reinterpret_cast<const float*>(parts0 + part * part_stride_bytes + lse_off_bytes) + row); };
+    // every part this row needs is requested before the first merge
+    uint4 cur = part_row(levels);
+    float l1 = part_lse(levels);
+    for (int l0 = levels - 1; l0 >= 0; l0 -= 4) {
+      uint4 nw[4];
+      float l2[4];
+      bool need[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int l = l0 - j;
+        need[j] = l >= 0 && ((i / (n >> (l + 1))) & 1);
+        nw[j] = make_uint4(0, 0, 0, 0);
+        l2[j] = 0.f;
+        if (need[j]) {
+          nw[j] = part_row(l);
+          l2[j] = part_lse(l);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (!need[j]) continue;
+        float w1, w2, lm;
+        if (exact) {
+          const float m2 = fmaxf(l1, l2[j]);
+          const float e1 = __expf(l1 - m2), e2 = __expf(l2[j] - m2);
+          w1 = e1 / (e1 + e2);
+          w2 = e2 / (e1 + e2);
+          lm = m2 + __logf(e1 + e2);
+        } else {
+          const float cf = round_to<T>(1.f / (1.f + __expf(l2[j] - l1)));
+          w1 = cf;
+          w2 = round_to<T>(1.f - cf);
+          lm = l1 - __logf(cf + 1.1920929e-07f);
+        }
+        const uint32_t ow[4] = {cur.x, cur.y, cur.z, cur.w}, pw[4] = {nw[j].x, nw[j].y, nw[j].z, nw[j].w};
+        uint32_t w[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const float2 old = unpack2<T>(ow[h]), mine = unpack2<T>(pw[h]);
+          w[h] = pack2<T>(w1 * old.x + w2 * mine.x, w1 * old.y + w2 * mine.y);
+        }
+        cur = make_uint4(w[0], w[1], w[2], w[3]);
+        l1 = lm;
+      }
+    }
+    *reinterpret_cast<uint4*>(o + row * dv + chunk * 8) = cur;
+    if (chunk == 0) lse[row] = l1;
+  }
+}
+
 static void fill_attn(const ha_causal_params& p, ha_attn_params& a) {
   a = ha_attn_params{};
   a.dtype = p.dtype;
@@ -259,7 +331,11 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
   a.flags = HA_FLAG_CAUSAL | (p.flags & HA_FLAG_FORCE_SIMT);
   a.segs_per_head = 1 << p.levels;
   a.span = pl.leaf; a.q_off = 0; a.k_off = 0; a.m_q = pl.leaf; a.m_k = pl.leaf;
-  if (p.keep_parts) { a.part_o = sv.part_o(p.levels); a.part_lse = sv.part_lse(p.levels); }
+  // A call that keeps the parts (16-bit tensors, tensor-core kernels) writes every part straight into its slot and merges
+  // them in one pass at the end; otherwise every rectangle merges into (o, lse) in its epilogue.
+  const bool deferred = p.keep_parts && p.levels > 0 && p.dtype != HA_FP32 && !(p.flags & HA_FLAG_FORCE_SIMT) && p.dv % 8 == 0 && 256 % p.dv == 0;
+  if (deferred) { a.o = sv.part_o(p.levels); a.lse = sv.part_lse(p.levels); }
+  else if (p.keep_parts) { a.part_o = sv.part_o(p.levels); a.part_lse = sv.part_lse(p.levels); }
   rc = ha_attn_fwd(&a, stream);
   if (side) HA_CUDA_OK(cudaStreamWaitEvent(main_st, side->join, 0), "ha_causal_fwd join");
   if (side) side_lock.unlock();
@@ -269,13 +345,31 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
     const int span = p.n >> l, m = span / 2;
     const bool exact = exact_deepest && l == p.levels - 1;
     a.mode = exact ? HA_MODE_FLASH : HA_MODE_HYPER;
-    a.flags = HA_FLAG_MERGE | (p.flags & (HA_FLAG_MERGE_EXACT | HA_FLAG_FORCE_SIMT)) | (exact ? 0 : (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_NO_WS)));
+    a.flags = (deferred ? 0 : HA_FLAG_MERGE | (p.flags & HA_FLAG_MERGE_EXACT)) | (p.flags & HA_FLAG_FORCE_SIMT) |
+              (exact ? 0 : (p.flags & (HA_FLAG_SMOOTH | HA_FLAG_NO_WS)));
     a.segs_per_head = 1 << l;
     a.span = span; a.q_off = m; a.k_off = 0; a.m_q = m; a.m_k = m;
     a.q_idx = exact ? nullptr : sv.q_idx(l); a.k_idx = exact ? nullptr : sv.k_idx(l); a.sample_idx = nullptr;
-    if (p.keep_parts) { a.part_o = sv.part_o(l); a.part_lse = sv.part_lse(l); }
+    if (deferred) { a.o = sv.part_o(l); a.lse = sv.part_lse(l); }
+    else if (p.keep_parts) { a.part_o = sv.part_o(l); a.part_lse = sv.part_lse(l); }
     rc = ha_attn_fwd(&a, stream);
     if (rc != HA_OK) return rc;
+  }
+  if (deferred) {
+    const int lpr = p.dv / 8;
+    const long long per_cta = 8LL * (32 / lpr) * 8;
+    const long long want = (pl.rows + per_cta - 1) / per_cta;
+    const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
+    const long long part_stride = (const uint8_t*)sv.part_o(1) - (const uint8_t*)sv.part_o(0);
+    const long long lse_off = (const uint8_t*)sv.part_lse(0) - (const uint8_t*)sv.part_o(0);
+    const int exact_merge = (p.flags & HA_FLAG_MERGE_EXACT) ? 1 : 0;
+    if (p.dtype == HA_BF16)
+      merge_parts_kernel<__nv_bfloat16><<<grid, 256, 0, main_st>>>((const uint8_t*)sv.part_o(0), part_stride, lse_off, p.levels, p.n, lpr,
+                                                                  (__nv_bfloat16*)p.o, p.lse, pl.rows, exact_merge);
+    else
+      merge_parts_kernel<__half><<<grid, 256, 0, main_st>>>((const uint8_t*)sv.part_o(0), part_stride, lse_off, p.levels, p.n, lpr, (__half*)p.o,
+                                                           p.lse, pl.rows, exact_merge);
+    HA_LAUNCHED("ha_causal_fwd merge");
   }
   return HA_OK;
 }
