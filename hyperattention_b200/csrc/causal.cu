@@ -83,9 +83,24 @@ static int make_plan(const ha_causal_params& p, CausalPlan& pl) {
 
 // delta of every part in one pass: dO is read once per row; the leaf part is needed by every row, the rectangle of
 // depth l only by rows in the second half of their span.  Output delta[part][B*H*n], part = depth, leaves last.
+// Both multi-part passes below are bound by instruction issue, not by DRAM (ncu: issue slots 67-71% busy at 28-35% of the
+// DRAM rate), so the index arithmetic is kept off the loop: a row's position inside its head advances by a constant
+// from one iteration to the next (one conditional subtraction instead of a 64-bit modulo), and with n a power of two
+// (log2n >= 0) the half-span test of a depth is a shift instead of a division.
+__device__ __forceinline__ int half_bit(int i, int n, int depth, int log2n) {
+  return (log2n >= 0 ? i >> (log2n - depth - 1) : i / (n >> (depth + 1))) & 1;
+}
+static int log2_if_pow2(int n) {
+  if (n <= 0 || (n & (n - 1))) return -1;
+  int l = 0;
+  while ((1 << l) < n) ++l;
+  return l;
+}
+
 template <typename T, int EPC>
 __global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ d_o, const uint8_t* __restrict__ parts0, long long part_stride_bytes,
-                                                          int levels, int n, int lpr, float* __restrict__ delta, long long total_rows) {
+                                                          int levels, int n, int lpr, float* __restrict__ delta, long long total_rows,
+                                                          int log2n) {
   const int lane = threadIdx.x & 31;
   const int rpw = 32 / lpr, chunk = lane % lpr, sub = lane / lpr;
   const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -93,18 +108,35 @@ __global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ 
   const int dv = lpr * EPC;
   constexpr int UN = 2;   // row groups per iteration
   constexpr int PG = 4;   // parts whose rows are requested together: UN * (PG + 1) independent 16-byte loads in flight per lane
+  const int step = (int)((n_warps * rpw * UN) % n);
+  int i[UN];
+#pragma unroll
+  for (int u = 0; u < UN; ++u) i[u] = (int)((warp_id * rpw * UN + u * rpw + sub) % n);
   for (long long base = warp_id * rpw * UN; base < total_rows; base += n_warps * rpw * UN) {
     long long row[UN];
     bool ok[UN];
-    int i[UN];
     uint4 g[UN];
 #pragma unroll
     for (int u = 0; u < UN; ++u) {
       row[u] = base + u * rpw + sub;
       ok[u] = row[u] < total_rows;
-      i[u] = ok[u] ? (int)(row[u] % n) : 0;
       g[u] = make_uint4(0, 0, 0, 0);
       if (ok[u]) g[u] = __ldg(reinterpret_cast<const uint4*>(d_o + row[u] * dv + chunk * EPC));
+    }
+    float gf[UN][8];      // this lane's dO elements, unpacked once for all parts
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const uint32_t gw[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        if constexpr (EPC == 8) {
+          const float2 fg = unpack2<T>(gw[w]);
+          gf[u][2 * w] = fg.x;
+          gf[u][2 * w + 1] = fg.y;
+        } else {
+          gf[u][w] = __uint_as_float(gw[w]);
+        }
+      }
     }
     for (int part0 = 0; part0 <= levels; part0 += PG) {
       bool need[PG][UN];
@@ -114,7 +146,7 @@ __global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ 
         const int part = part0 + pp;
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
-          need[pp][u] = part <= levels && ok[u] && (part == levels || ((i[u] / (n >> (part + 1))) & 1));
+          need[pp][u] = part <= levels && ok[u] && (part == levels || half_bit(i[u], n, part, log2n));
           a[pp][u] = make_uint4(0, 0, 0, 0);
           if (need[pp][u])
             a[pp][u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(parts0 + part * part_stride_bytes) + row[u] * dv + chunk * EPC));
@@ -125,22 +157,29 @@ __global__ void __launch_bounds__(256) delta_parts_kernel(const T* __restrict__ 
         const int part = part0 + pp;
 #pragma unroll
         for (int u = 0; u < UN; ++u) {
+          // a warp's rows are consecutive: they nearly always need the same parts, and a part nobody needs is skipped whole
+          if (!__any_sync(0xffffffffu, need[pp][u])) continue;
           float s = 0.f;
-          const uint32_t aw[4] = {a[pp][u].x, a[pp][u].y, a[pp][u].z, a[pp][u].w}, gw[4] = {g[u].x, g[u].y, g[u].z, g[u].w};
+          const uint32_t aw[4] = {a[pp][u].x, a[pp][u].y, a[pp][u].z, a[pp][u].w};
 #pragma unroll
           for (int w = 0; w < 4; ++w) {
             if constexpr (EPC == 8) {
-              const float2 fa = unpack2<T>(aw[w]), fg = unpack2<T>(gw[w]);
-              s = fmaf(fa.x, fg.x, s);
-              s = fmaf(fa.y, fg.y, s);
+              const float2 fa = unpack2<T>(aw[w]);
+              s = fmaf(fa.x, gf[u][2 * w], s);
+              s = fmaf(fa.y, gf[u][2 * w + 1], s);
             } else {
-              s = fmaf(__uint_as_float(aw[w]), __uint_as_float(gw[w]), s);
+              s = fmaf(__uint_as_float(aw[w]), gf[u][w], s);
             }
           }
           for (int off = lpr >> 1; off >= 1; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
           if (need[pp][u] && chunk == 0) delta[(long long)part * total_rows + row[u]] = s;
         }
       }
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      i[u] += step;
+      if (i[u] >= n) i[u] -= n;
     }
   }
 }
@@ -172,16 +211,19 @@ struct SavedLayout {
 template <typename T>
 __global__ void __launch_bounds__(256) merge_parts_kernel(const uint8_t* __restrict__ parts0, long long part_stride_bytes, long long lse_off_bytes,
                                                           int levels, int n, int lpr, T* __restrict__ o, float* __restrict__ lse,
-                                                          long long total_rows, int exact) {
+                                                          long long total_rows, int exact, int log2n) {
   const int lane = threadIdx.x & 31;
   const int rpw = 32 / lpr, chunk = lane % lpr, sub = lane / lpr;
   const long long warp_id = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
   const int dv = lpr * 8;
+  const int step = (int)((n_warps * rpw) % n);
+  int i = (int)((warp_id * rpw + sub) % n) - step;
   for (long long base = warp_id * rpw; base < total_rows; base += n_warps * rpw) {
+    i += step;
+    if (i >= n) i -= n;
     const long long row = base + sub;
     if (row >= total_rows) continue;
-    const int i = (int)(row % n);
     auto part_row = [&](int part) { return __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(parts0 + part * part_stride_bytes) + row * dv + chunk * 8)); };
     auto part_lse = [&](int part) { return __ldg(reinterpret_cast<const float*>(parts0 + part * part_stride_bytes + lse_off_bytes) + row); };
     // every part this row needs is requested before the first merge
@@ -194,7 +236,7 @@ __global__ void __launch_bounds__(256) merge_parts_kernel(const uint8_t* __restr
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int l = l0 - j;
-        need[j] = l >= 0 && ((i / (n >> (l + 1))) & 1);
+        need[j] = l >= 0 && half_bit(i, n, l, log2n);
         nw[j] = make_uint4(0, 0, 0, 0);
         l2[j] = 0.f;
         if (need[j]) {
@@ -365,10 +407,10 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
     const int exact_merge = (p.flags & HA_FLAG_MERGE_EXACT) ? 1 : 0;
     if (p.dtype == HA_BF16)
       merge_parts_kernel<__nv_bfloat16><<<grid, 256, 0, main_st>>>((const uint8_t*)sv.part_o(0), part_stride, lse_off, p.levels, p.n, lpr,
-                                                                  (__nv_bfloat16*)p.o, p.lse, pl.rows, exact_merge);
+                                                                  (__nv_bfloat16*)p.o, p.lse, pl.rows, exact_merge, log2_if_pow2(p.n));
     else
       merge_parts_kernel<__half><<<grid, 256, 0, main_st>>>((const uint8_t*)sv.part_o(0), part_stride, lse_off, p.levels, p.n, lpr, (__half*)p.o,
-                                                           p.lse, pl.rows, exact_merge);
+                                                           p.lse, pl.rows, exact_merge, log2_if_pow2(p.n));
     HA_LAUNCHED("ha_causal_fwd merge");
   }
   return HA_OK;
@@ -420,11 +462,11 @@ int ha_causal_bwd(const ha_causal_params* pp, void* stream) {
       long long want = (pl.rows + per_cta - 1) / per_cta;
       const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
       if (p.dtype == HA_BF16)
-        delta_parts_kernel<__nv_bfloat16, 8><<<grid, 256, 0, st>>>((const __nv_bfloat16*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows);
+        delta_parts_kernel<__nv_bfloat16, 8><<<grid, 256, 0, st>>>((const __nv_bfloat16*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows, log2_if_pow2(p.n));
       else if (p.dtype == HA_FP16)
-        delta_parts_kernel<__half, 8><<<grid, 256, 0, st>>>((const __half*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows);
+        delta_parts_kernel<__half, 8><<<grid, 256, 0, st>>>((const __half*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows, log2_if_pow2(p.n));
       else
-        delta_parts_kernel<float, 4><<<grid, 256, 0, st>>>((const float*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows);
+        delta_parts_kernel<float, 4><<<grid, 256, 0, st>>>((const float*)p.d_o, (const uint8_t*)sv.part_o(0), part_stride, p.levels, p.n, lpr, delta, pl.rows, log2_if_pow2(p.n));
       HA_LAUNCHED("ha_causal_bwd delta");
       fused_parts = true;
     }
