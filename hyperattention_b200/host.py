@@ -26,7 +26,7 @@ class HostStream:
     heads_per_chunk: heads per chunk (default: at least four chunks per call, so that copy-in, kernels and copy-out
     overlap, and at most about 160 MB of inputs per chunk: the first copy-in and the last copy-out overlap with nothing, so
     chunks are kept small -- measured at 32 heads x 131072 x 64 bf16 over PCIe 5: 8 heads per chunk 56 ms, 4 49 ms, 2 48 ms,
-    1 62 ms per forward + backward).
+    1 62 ms per forward + backward); the first and the last chunk are half that size.
     Two chunks of inputs are resident at a time; outputs are written into pinned host buffers that are kept and
     reused between calls (pass out=... to supply your own)."""
 
@@ -52,6 +52,13 @@ class HostStream:
         if hpc is None:
             per_head = max(1, B * n * d * q.element_size() * n_inputs)
             hpc = max(1, min(max(1, H // 4), (160 << 20) // per_head))
+            # the first chunk's copy-in and the last chunk's copy-out are the two transfers nothing overlaps: half-size chunks
+            # at both ends
+            edge = max(1, hpc // 2)
+            if edge < hpc and H >= 2 * edge + hpc:
+                cuts = [0, edge] + list(range(edge + hpc, H - edge, hpc)) + [H - edge, H]
+                cuts = sorted(set(cuts))
+                return [(a, b) for a, b in zip(cuts[:-1], cuts[1:])]
         return [(h0, min(H, h0 + hpc)) for h0 in range(0, H, hpc)]
 
     def _host_out(self, key, like, shape):
