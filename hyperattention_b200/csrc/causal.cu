@@ -311,10 +311,22 @@ int64_t ha_causal_saved_bytes(const ha_causal_params* p) {
   return s.total();
 }
 
+// Can the merges of this call run as one pass over the parts (merge_parts_kernel)?
+static bool merges_deferrable(const ha_causal_params& p) {
+  return p.levels > 0 && p.dtype != HA_FP32 && !(p.flags & HA_FLAG_FORCE_SIMT) && p.dv % 8 == 0 && 256 % p.dv == 0;
+}
+// A forward that keeps no parts for a backward still runs that way when the parts fit a scratch budget: a merging
+// rectangle launch costs a third more than a plain one (config 2 forward: 8.6 -> 7.7 ms).
+static long long scratch_part_bytes(const ha_causal_params& p, const CausalPlan& pl) {
+  if (p.keep_parts || !merges_deferrable(p)) return 0;
+  const long long bytes = (long long)(p.levels + 1) * (align256(pl.part_o_bytes) + align256(pl.part_lse_bytes));
+  return bytes <= (16LL << 30) ? bytes : 0;
+}
+
 int64_t ha_causal_scratch_bytes(const ha_causal_params* p, int32_t backward) {
   CausalPlan pl;
   if (!p || make_plan(*p, pl) != HA_OK) return -1;
-  if (!backward) return 2 * align256(pl.rows * 4) + align256(pl.sort_ws);
+  if (!backward) return 2 * align256(pl.rows * 4) + align256(pl.sort_ws) + scratch_part_bytes(*p, pl);
   return align256(pl.rows * p->d * 4) + align256(pl.rows_k * p->d * 4) + align256(pl.rows_k * p->dv * 4) + align256(pl.rows * 4 * (p->levels + 1));
 }
 
@@ -375,8 +387,14 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
   a.span = pl.leaf; a.q_off = 0; a.k_off = 0; a.m_q = pl.leaf; a.m_k = pl.leaf;
   // A call that keeps the parts (16-bit tensors, tensor-core kernels) writes every part straight into its slot and merges
   // them in one pass at the end; otherwise every rectangle merges into (o, lse) in its epilogue.
-  const bool deferred = p.keep_parts && p.levels > 0 && p.dtype != HA_FP32 && !(p.flags & HA_FLAG_FORCE_SIMT) && p.dv % 8 == 0 && 256 % p.dv == 0;
-  if (deferred) { a.o = sv.part_o(p.levels); a.lse = sv.part_lse(p.levels); }
+  const long long in_scratch = scratch_part_bytes(p, pl);
+  const bool deferred = merges_deferrable(p) && (p.keep_parts || in_scratch > 0);
+  // the parts' slots: in the saved buffer (kept for the backward) or, for a call that keeps nothing, in the scratch
+  uint8_t* const slots = !deferred ? nullptr : p.keep_parts ? (uint8_t*)sv.part_o(0) : (uint8_t*)p.scratch + 2 * align256(pl.rows * 4) + align256(pl.sort_ws);
+  const long long slot_stride = align256(pl.part_o_bytes) + align256(pl.part_lse_bytes), slot_lse = align256(pl.part_o_bytes);
+  auto slot_o = [&](int part) -> void* { return slots + part * slot_stride; };
+  auto slot_lse_of = [&](int part) -> float* { return (float*)(slots + part * slot_stride + slot_lse); };
+  if (deferred) { a.o = slot_o(p.levels); a.lse = slot_lse_of(p.levels); }
   else if (p.keep_parts) { a.part_o = sv.part_o(p.levels); a.part_lse = sv.part_lse(p.levels); }
   rc = ha_attn_fwd(&a, stream);
   if (side) HA_CUDA_OK(cudaStreamWaitEvent(main_st, side->join, 0), "ha_causal_fwd join");
@@ -392,7 +410,7 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
     a.segs_per_head = 1 << l;
     a.span = span; a.q_off = m; a.k_off = 0; a.m_q = m; a.m_k = m;
     a.q_idx = exact ? nullptr : sv.q_idx(l); a.k_idx = exact ? nullptr : sv.k_idx(l); a.sample_idx = nullptr;
-    if (deferred) { a.o = sv.part_o(l); a.lse = sv.part_lse(l); }
+    if (deferred) { a.o = slot_o(l); a.lse = slot_lse_of(l); }
     else if (p.keep_parts) { a.part_o = sv.part_o(l); a.part_lse = sv.part_lse(l); }
     rc = ha_attn_fwd(&a, stream);
     if (rc != HA_OK) return rc;
@@ -402,14 +420,13 @@ int ha_causal_fwd(const ha_causal_params* pp, void* stream) {
     const long long per_cta = 8LL * (32 / lpr) * 8;
     const long long want = (pl.rows + per_cta - 1) / per_cta;
     const int grid = (int)(want < 148LL * 16 ? want : 148LL * 16);
-    const long long part_stride = (const uint8_t*)sv.part_o(1) - (const uint8_t*)sv.part_o(0);
-    const long long lse_off = (const uint8_t*)sv.part_lse(0) - (const uint8_t*)sv.part_o(0);
+    const long long part_stride = slot_stride, lse_off = slot_lse;
     const int exact_merge = (p.flags & HA_FLAG_MERGE_EXACT) ? 1 : 0;
     if (p.dtype == HA_BF16)
-      merge_parts_kernel<__nv_bfloat16><<<grid, 256, 0, main_st>>>((const uint8_t*)sv.part_o(0), part_stride, lse_off, p.levels, p.n, lpr,
+      merge_parts_kernel<__nv_bfloat16><<<grid, 256, 0, main_st>>>((const uint8_t*)slots, part_stride, lse_off, p.levels, p.n, lpr,
                                                                   (__nv_bfloat16*)p.o, p.lse, pl.rows, exact_merge, log2_if_pow2(p.n));
     else
-      merge_parts_kernel<__half><<<grid, 256, 0, main_st>>>((const uint8_t*)sv.part_o(0), part_stride, lse_off, p.levels, p.n, lpr, (__half*)p.o,
+      merge_parts_kernel<__half><<<grid, 256, 0, main_st>>>((const uint8_t*)slots, part_stride, lse_off, p.levels, p.n, lpr, (__half*)p.o,
                                                            p.lse, pl.rows, exact_merge, log2_if_pow2(p.n));
     HA_LAUNCHED("ha_causal_fwd merge");
   }

@@ -243,6 +243,9 @@ typedef struct {
 } ha_causal_params;
 
 int64_t ha_causal_saved_bytes(const ha_causal_params* p);
+/* Scratch of one call (contents undefined afterwards).  The forward's includes room for every part's (o, lse) when the call
+ * keeps no parts for a backward and they fit 16 GB: the merges then run as one pass over the parts instead of in every
+ * rectangle's epilogue. */
 int64_t ha_causal_scratch_bytes(const ha_causal_params* p, int32_t backward);
 int ha_causal_fwd(const ha_causal_params* p, void* stream);
 int ha_causal_bwd(const ha_causal_params* p, void* stream);
